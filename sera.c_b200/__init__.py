@@ -1,0 +1,328 @@
+"""Host-side mirror of the q3attn C ABI (include/q3_attn.h) for Python callers.
+
+The product is libq3attn.so; this module only loads it with ctypes and wraps
+its handles so tests, the benchmark and a Python host can drive the path with
+torch tensors as device memory. There is no CPU implementation here: if the
+library is missing or no CUDA device is present, the calls fail loudly.
+
+The directory name contains a dot, so import it through the repository's
+`__graft_entry__.load_package()` (module name `sera_c_b200`).
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from ._lib import ERRLEN, Q3Error, bind, lib_path  # noqa: F401
+
+PAGE = 16
+D = 128
+G = 8
+
+_c_u32p = ctypes.POINTER(ctypes.c_uint32)
+
+
+def _u32(a):
+    a = np.ascontiguousarray(a, dtype=np.uint32)
+    return a, a.ctypes.data_as(_c_u32p)
+
+
+def _ptr(t):
+    """Device pointer of a torch tensor (or None)."""
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "need a contiguous CUDA tensor"
+    return ctypes.c_void_p(t.data_ptr())
+
+
+class _DevView:
+    """Exposes raw device memory owned by the library to torch."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {
+            "shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+            "version": 2}
+
+
+class AttnConfig(ctypes.Structure):
+    _fields_ = [("num_layers", ctypes.c_uint32), ("n_heads", ctypes.c_uint32),
+                ("n_kv_heads", ctypes.c_uint32), ("head_dim", ctypes.c_uint32),
+                ("rms_eps", ctypes.c_float), ("rope_theta", ctypes.c_double),
+                ("max_positions", ctypes.c_uint32), ("max_tokens", ctypes.c_uint32),
+                ("num_pages", ctypes.c_uint32), ("out_fp32", ctypes.c_uint32),
+                ("device", ctypes.c_int)]
+
+
+class AttnStats(ctypes.Structure):
+    _fields_ = [("cuda_allocations", ctypes.c_uint64), ("cuda_frees", ctypes.c_uint64),
+                ("host_syncs", ctypes.c_uint64), ("kernel_launches", ctypes.c_uint64),
+                ("pages_total", ctypes.c_uint64), ("pages_free", ctypes.c_uint64),
+                ("pool_bytes", ctypes.c_uint64), ("workspace_bytes", ctypes.c_uint64),
+                ("device_status", ctypes.c_uint32)]
+
+
+class SuffixItem(ctypes.Structure):
+    _fields_ = [("branch", ctypes.c_uint32), ("token_count", ctypes.c_uint32)]
+
+
+class SchedSegmentInfo(ctypes.Structure):
+    _fields_ = [("cta", ctypes.c_uint32), ("tok0", ctypes.c_uint32),
+                ("kv_head", ctypes.c_uint32), ("tile_begin", ctypes.c_uint32),
+                ("tile_end", ctypes.c_uint32), ("shared_tiles", ctypes.c_uint32),
+                ("partial_slot", ctypes.c_int32)]
+
+
+class SchedSummary(ctypes.Structure):
+    _fields_ = [("grid", ctypes.c_uint32), ("n_segments", ctypes.c_uint32),
+                ("n_merges", ctypes.c_uint32), ("n_slots", ctypes.c_uint32),
+                ("total_key_tiles", ctypes.c_uint64)]
+
+
+_LIB = None
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary)
+    return _LIB
+
+
+def _call(fn, *args):
+    """Invoke an ABI function that ends with (char *error, size_t error_len)."""
+    err = ctypes.create_string_buffer(ERRLEN)
+    r = fn(*args, err, ERRLEN)
+    failed = (r is None) or (r is False) or (isinstance(r, int) and not isinstance(r, bool) and r < 0)
+    if failed:
+        raise Q3Error(err.value.decode() or "%s failed" % fn.__name__)
+    return r
+
+
+class Runtime:
+    """q3_attn_runtime: stream, geometry, KV page pool, RoPE table, workspace."""
+
+    def __init__(self, num_layers, n_heads, n_kv_heads, max_positions, max_tokens,
+                 num_pages, device=0, rms_eps=1e-6, rope_theta=1e6, head_dim=D,
+                 out_fp32=False):
+        self.cfg = AttnConfig(num_layers, n_heads, n_kv_heads, head_dim, rms_eps,
+                              rope_theta, max_positions, max_tokens, num_pages,
+                              1 if out_fp32 else 0, device)
+        self.h = _call(lib().q3_attn_create, ctypes.byref(self.cfg))
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().q3_attn_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_qk_norm(self, layer, q_w, k_w):
+        q_w = np.ascontiguousarray(q_w, np.float32)
+        k_w = np.ascontiguousarray(k_w, np.float32)
+        _call(lib().q3_attn_set_qk_norm, self.h, layer,
+              q_w.ctypes.data_as(ctypes.POINTER(ctypes.c_float)),
+              k_w.ctypes.data_as(ctypes.POINTER(ctypes.c_float)))
+
+    @property
+    def stream_ptr(self):
+        return lib().q3_attn_stream(self.h)
+
+    def torch_stream(self):
+        import torch
+        return torch.cuda.ExternalStream(self.stream_ptr, device=self.cfg.device)
+
+    def synchronize(self):
+        _call(lib().q3_attn_synchronize, self.h)
+
+    def stats(self):
+        s = AttnStats()
+        lib().q3_attn_get_stats(self.h, ctypes.byref(s))
+        return s
+
+    def alloc_pages(self, n):
+        out = np.empty(n, np.uint32)
+        _call(lib().q3_pages_alloc, self.h, n, out.ctypes.data_as(_c_u32p))
+        return out
+
+    def free_pages(self, pages):
+        a, p = _u32(pages)
+        lib().q3_pages_free(self.h, p, len(a))
+
+    def pool(self):
+        """(K, V) page pools as torch f16 tensors [L, Hkv, num_pages, 16, 128]."""
+        import torch
+        c = self.cfg
+        shape = (c.num_layers, c.n_kv_heads, c.num_pages, PAGE, D)
+        k = torch.as_tensor(_DevView(lib().q3_pages_k(self.h), shape, "<f2"),
+                            device="cuda:%d" % c.device)
+        v = torch.as_tensor(_DevView(lib().q3_pages_v(self.h), shape, "<f2"),
+                            device="cuda:%d" % c.device)
+        return k, v
+
+    def qknorm_rope_kvwrite(self, layer, q, k, v, rope_pos, dst_page, dst_slot, q_out):
+        tokens = (q if q is not None else k).shape[0]
+        _call(lib().q3_cuda_qknorm_rope_kvwrite, self.h, layer, _ptr(q), _ptr(k), _ptr(v),
+              tokens, _ptr(rope_pos), _ptr(dst_page), _ptr(dst_slot), _ptr(q_out))
+
+
+class Prefix:
+    """q3_prefix_kv: the shared, sealed prefix (also: any single sequence)."""
+
+    def __init__(self, rt, capacity_tokens, pages=None):
+        self.rt = rt
+        if pages is None:
+            self.h = _call(lib().q3_prefix_create, rt.h, capacity_tokens)
+        else:
+            a, p = _u32(pages)
+            assert len(a) >= (capacity_tokens + PAGE - 1) // PAGE
+            self.h = _call(lib().q3_prefix_create_with_pages, rt.h, capacity_tokens, p)
+        self.capacity = capacity_tokens
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().q3_prefix_destroy(self.h)
+            self.h = None
+
+    def prefill_layer(self, layer, q, k, v, out):
+        _call(lib().q3_prefix_prefill_layer, self.h, layer, _ptr(q), _ptr(k), _ptr(v),
+              q.shape[0], _ptr(out))
+
+    def advance(self, tokens):
+        _call(lib().q3_prefix_advance, self.h, tokens)
+
+    def set_resident(self, token_count):
+        _call(lib().q3_prefix_set_resident, self.h, token_count)
+
+    def seal(self):
+        _call(lib().q3_prefix_seal, self.h)
+
+    @property
+    def token_count(self):
+        return lib().q3_prefix_token_count(self.h)
+
+    def kv_bytes(self):
+        return lib().q3_prefix_kv_bytes(self.h)
+
+    def page_table(self):
+        n = (self.capacity + PAGE - 1) // PAGE
+        p = lib().q3_prefix_page_table(self.h)
+        return np.ctypeslib.as_array(p, shape=(n,)).copy()
+
+
+class BranchSet:
+    """q3_branch_set: per-branch suffix pages, taken once."""
+
+    def __init__(self, prefix, max_branches, max_suffix_tokens):
+        self.prefix = prefix
+        self.h = _call(lib().q3_branch_set_create, prefix.h, max_branches,
+                       max_suffix_tokens)
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().q3_branch_set_destroy(self.h)
+            self.h = None
+
+    def acquire(self):
+        return _call(lib().q3_branch_acquire, self.h)
+
+    def release(self, b):
+        lib().q3_branch_release(self.h, b)
+
+    def page_table(self):
+        nb = lib().q3_branch_set_max_branches(self.h)
+        pp = lib().q3_branch_set_pages_per_branch(self.h)
+        p = lib().q3_branch_set_page_table(self.h)
+        return np.ctypeslib.as_array(p, shape=(nb, pp)).copy()
+
+    def kv_bytes(self):
+        return lib().q3_branch_set_kv_bytes(self.h)
+
+
+class PackPlan:
+    """q3_pack_plan: staged q3_pack_view + launch schedule of one suffix batch."""
+
+    def __init__(self, prefix, branch_set, items):
+        """items: list of (branch handle, token_count)."""
+        arr = (SuffixItem * len(items))(*[SuffixItem(b, n) for b, n in items])
+        self.prefix, self.set = prefix, branch_set
+        self.h = _call(lib().q3_pack_plan_create, prefix.h, branch_set.h, arr, len(items))
+        self.tokens = lib().q3_pack_plan_tokens(self.h)
+        self.branches = len(items)
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().q3_pack_plan_destroy(self.h)
+            self.h = None
+
+    def _arr(self, fn, n):
+        return np.ctypeslib.as_array(fn(self.h), shape=(n,)).copy()
+
+    def descriptors(self):
+        L = lib()
+        return dict(
+            token_positions=self._arr(L.q3_pack_plan_token_positions, self.tokens),
+            token_branch=self._arr(L.q3_pack_plan_token_branch, self.tokens),
+            token_local_pos=self._arr(L.q3_pack_plan_token_local_pos, self.tokens),
+            branch_offsets=self._arr(L.q3_pack_plan_branch_offsets, self.branches + 1))
+
+    def attention_layer(self, layer, q, k, v, out):
+        _call(lib().q3_suffix_attention_layer, self.h, layer, _ptr(q), _ptr(k), _ptr(v),
+              _ptr(out))
+
+    def attention_layer_host(self, layer, q, k, v, out):
+        """q/k/v/out: pinned host torch tensors."""
+        _call(lib().q3_suffix_attention_layer_host, self.h, layer,
+              ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+              ctypes.c_void_p(v.data_ptr()), ctypes.c_void_p(out.data_ptr()))
+
+
+class DecodePlan:
+    """q3_decode_plan: page lists and split-KV work list of a decode batch."""
+
+    def __init__(self, rt, ctx_lens, page_indptr, page_indices):
+        a, pa = _u32(ctx_lens)
+        b, pb = _u32(page_indptr)
+        c, pc = _u32(page_indices)
+        self.rt = rt
+        self.num_seqs = len(a)
+        self.h = _call(lib().q3_decode_plan_create, rt.h, pa, pb, pc, len(a))
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().q3_decode_plan_destroy(self.h)
+            self.h = None
+
+    def attention_layer(self, layer, q, k_new, v_new, out):
+        _call(lib().q3_decode_attention_layer, self.h, layer, _ptr(q), _ptr(k_new),
+              _ptr(v_new), _ptr(out))
+
+
+def pack_suffix_host(items, prefix_len, max_branches, max_suffix):
+    """q3_pack_suffix_host: the reference's q3_decide_run packing, pure host."""
+    arr = (SuffixItem * len(items))(*[SuffixItem(b, n) for b, n in items])
+    total = int(sum(n for _, n in items))
+    pos = np.zeros(max(total, 1), np.uint32)
+    br = np.zeros(max(total, 1), np.uint32)
+    lp = np.zeros(max(total, 1), np.uint32)
+    off = np.zeros(len(items) + 1, np.uint32)
+    n = _call(lib().q3_pack_suffix_host, arr, len(items), prefix_len, max_branches,
+              max_suffix, pos.ctypes.data_as(_c_u32p), br.ctypes.data_as(_c_u32p),
+              lp.ctypes.data_as(_c_u32p), off.ctypes.data_as(_c_u32p))
+    return dict(tokens=int(n), token_positions=pos[:n], token_branch=br[:n],
+                token_local_pos=lp[:n], branch_offsets=off)
+
+
+def schedule_describe(row_tag, row_lp, n_kv_heads, shared_len, pages_per_branch,
+                      n_branches, num_ctas, max_slots=1 << 20):
+    a, pa = _u32(row_tag)
+    b, pb = _u32(row_lp)
+    summ = SchedSummary()
+    cap = 4 * num_ctas + 4 * ((len(a) + 31) // 32) * n_kv_heads + 16
+    segs = (SchedSegmentInfo * cap)()
+    _call(lib().q3_schedule_describe, len(a), n_kv_heads, shared_len, pa, pb,
+          pages_per_branch, n_branches, num_ctas, max_slots, ctypes.byref(summ), segs, cap)
+    return summ, [segs[i] for i in range(min(cap, summ.n_segments))]

@@ -1,0 +1,108 @@
+"""ctypes signatures for every symbol include/q3_attn.h declares."""
+import ctypes
+import os
+
+ERRLEN = 512
+PKG = os.path.dirname(os.path.abspath(__file__))
+
+
+class Q3Error(RuntimeError):
+    """An ABI call returned false / NULL / -1; the message is the library's."""
+
+
+def lib_path():
+    return os.path.join(PKG, "libq3attn.so")
+
+
+def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
+    path = lib_path()
+    if not os.path.exists(path):
+        raise Q3Error("libq3attn.so is not built (run python sera.c_b200/build.py); "
+                      "there is no fallback path")
+    L = ctypes.CDLL(path)
+    vp, u32, u64, sz = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_size_t
+    fp = ctypes.POINTER(ctypes.c_float)
+    up = ctypes.POINTER(ctypes.c_uint32)
+    cf = ctypes.c_float
+    err = [ctypes.c_char_p, sz]
+    b = ctypes.c_bool
+
+    def sig(name, res, args):
+        f = getattr(L, name)
+        f.restype = res
+        f.argtypes = args
+        return f
+
+    # ---- part 1: reference surface
+    sig("q3_kv_cache_init", vp, [u32, u32, u32, u32] + err)
+    sig("q3_kv_cache_reserve", b, [vp, u32] + err)
+    sig("q3_kv_cache_reset", None, [vp])
+    sig("q3_kv_cache_destroy", None, [vp])
+    sig("q3_kv_cache_length", u32, [vp])
+    sig("q3_kv_cache_alias", vp, [vp, vp, u32, u32, u32, u32, u32] + err)
+    sig("q3_kv_cache_advance", None, [vp, u32])
+    sig("q3_kv_cache_k", vp, [vp])
+    sig("q3_kv_cache_v", vp, [vp])
+    sig("q3_cuda_rms_norm", b, [vp, vp, u32, u32, cf, vp, vp] + err)
+    sig("q3_cuda_rope", b, [vp, vp, u32, u32, u32, u32, u32, vp, vp] + err)
+    sig("q3_cuda_rope_positions", b, [vp, vp, u32, u32, u32, u32, vp, vp, vp] + err)
+    sig("q3_cuda_attention", b,
+        [vp, vp, vp, u32, u32, u32, u32, u32, vp, u32, cf, vp, vp] + err)
+    sig("q3_cuda_attention_segmented", b,
+        [vp, vp, vp, u32, u32, vp, vp, u32, u32, u32, vp, vp, u32, u32, u32, u32, cf, vp,
+         vp] + err)
+    sig("q3_cuda_kv_scatter", b, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp] + err)
+    sig("q3_kv_bytes_for_tokens", sz, [u32, u32, u32, u32])
+    # ---- part 2: native paged path
+    sig("q3_attn_create", vp, [ctypes.POINTER(AttnConfig)] + err)
+    sig("q3_attn_destroy", None, [vp])
+    sig("q3_attn_set_qk_norm", b, [vp, u32, fp, fp] + err)
+    sig("q3_attn_stream", vp, [vp])
+    sig("q3_attn_synchronize", b, [vp] + err)
+    sig("q3_attn_get_stats", None, [vp, ctypes.POINTER(AttnStats)])
+    sig("q3_pages_alloc", b, [vp, u32, up] + err)
+    sig("q3_pages_free", None, [vp, up, u32])
+    sig("q3_pages_k", vp, [vp])
+    sig("q3_pages_v", vp, [vp])
+    sig("q3_prefix_create", vp, [vp, u32] + err)
+    sig("q3_prefix_create_with_pages", vp, [vp, u32, up] + err)
+    sig("q3_prefix_prefill_layer", b, [vp, u32, vp, vp, vp, u32, vp] + err)
+    sig("q3_prefix_advance", b, [vp, u32] + err)
+    sig("q3_prefix_set_resident", b, [vp, u32] + err)
+    sig("q3_prefix_seal", b, [vp] + err)
+    sig("q3_prefix_destroy", None, [vp])
+    sig("q3_prefix_token_count", u32, [vp])
+    sig("q3_prefix_kv_bytes", sz, [vp])
+    sig("q3_prefix_copy_bytes", u64, [vp])
+    sig("q3_prefix_allocations", u64, [vp])
+    sig("q3_prefix_page_table", up, [vp])
+    sig("q3_branch_set_create", vp, [vp, u32, u32] + err)
+    sig("q3_branch_acquire", ctypes.c_int32, [vp] + err)
+    sig("q3_branch_reset", None, [vp, ctypes.c_int32])
+    sig("q3_branch_release", None, [vp, ctypes.c_int32])
+    sig("q3_branch_set_destroy", None, [vp])
+    sig("q3_branch_set_kv_bytes", sz, [vp])
+    sig("q3_branch_set_max_branches", u32, [vp])
+    sig("q3_branch_set_max_suffix", u32, [vp])
+    sig("q3_branch_set_page_table", up, [vp])
+    sig("q3_branch_set_pages_per_branch", u32, [vp])
+    sig("q3_pack_suffix_host", ctypes.c_int64,
+        [ctypes.POINTER(SuffixItem), u32, u32, u32, u32, up, up, up, up] + err)
+    sig("q3_pack_plan_create", vp, [vp, vp, ctypes.POINTER(SuffixItem), u32] + err)
+    sig("q3_pack_plan_destroy", None, [vp])
+    sig("q3_pack_plan_tokens", u32, [vp])
+    sig("q3_pack_plan_token_positions", up, [vp])
+    sig("q3_pack_plan_token_branch", up, [vp])
+    sig("q3_pack_plan_token_local_pos", up, [vp])
+    sig("q3_pack_plan_branch_offsets", up, [vp])
+    sig("q3_suffix_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_suffix_attention_layer_host", b, [vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_decode_plan_create", vp, [vp, up, up, up, u32] + err)
+    sig("q3_decode_plan_destroy", None, [vp])
+    sig("q3_decode_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_cuda_qknorm_rope_kvwrite", b, [vp, u32, vp, vp, vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_schedule_describe", b,
+        [u32, u32, u32, up, up, u32, u32, u32, u32, ctypes.POINTER(SchedSummary),
+         ctypes.POINTER(SchedSegmentInfo), u32] + err)
+    sig("q3_attn_version", ctypes.c_char_p, [])
+    return L

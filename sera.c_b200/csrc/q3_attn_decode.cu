@@ -1,0 +1,394 @@
+/* q3_attn_decode.cu - paged decode attention: many independent sequences, one
+ * query token each, f16 KV in 16-token pages (the reference's q3_cuda_attention
+ * with tokens == 1 over a cache, ref: src/q3_forward.cu:218-290,722-755, on a
+ * paged pool).
+ *
+ * HBM-bound: 8 query rows per KV head against up to 16K keys, 8 FLOP per KV
+ * byte. The design is therefore about keeping pages in flight:
+ *   - every sequence is cut into chunks of <= 64 pages (split-KV); a CTA owns
+ *     one (chunk, KV head) and writes either the final bf16 rows (single
+ *     chunk) or fp32 partials + (max, sum) that decode_merge_kernel combines
+ *     with log-sum-exp;
+ *   - one producer warp streams K and V pages with TMA (128-byte swizzle, two
+ *     2 KiB boxes per page per operand) through a 3-stage ring of 4 pages
+ *     (32 KiB per stage; two CTAs per SM keep ~128 KiB in flight per SM);
+ *   - four consumer warps take one page each: S = Q K^T and O += P V with
+ *     mma.sync m16n8k16 (rows 8..15 of the M tile are padding; tensor-core
+ *     rate is irrelevant here), ldmatrix reads the swizzled pages without
+ *     bank conflicts, online softmax in registers with quad shuffles.
+ * Algorithmic bytes: every K and V page of the context once (4 KiB per page
+ * per head per operand) + q in + out.
+ */
+#include "q3_internal.h"
+#include "q3_ptx.cuh"
+
+using namespace q3ptx;
+
+namespace {
+
+constexpr uint32_t kDecStages = 3;
+constexpr uint32_t kDecTilePages = 4;
+constexpr uint32_t kDecStageBytes = kDecTilePages * 2 * 4096; /* K + V */
+constexpr uint32_t kDecThreads = 160;
+constexpr uint32_t kDecSmemRing = kDecStages * kDecStageBytes;
+/* The per-warp partials (O + (m,l)) are combined through the ring's first
+ * bytes once every page has been consumed, so two CTAs fit in one SM. */
+constexpr uint32_t kDecSmemCombine = 4 * 8 * 132 * 4 + 4 * 8 * 8;
+static_assert(kDecSmemCombine <= kDecSmemRing, "combine buffer aliases the ring");
+constexpr uint32_t kDecSmemTotal = kDecSmemRing + 256 + 1024;
+
+struct DecodeParams {
+    const q3_decode_work *work;
+    const uint32_t *seq_work_begin;
+    const uint32_t *ctx_lens;
+    const uint32_t *page_indptr;
+    const uint32_t *page_indices;
+    const __half *q2;          /* [seqs][n_heads][128] normalised, roped */
+    uint32_t n_heads, n_kv_heads, num_pages;
+    uint32_t pool_row_base, pool_rows_total;
+    uint32_t extra_token;
+    float scale_log2;
+    uint32_t out_fp32;
+    void *out;
+    float *part_o;             /* [work*Hkv + h][8][128] */
+    float2 *part_ml;           /* [work*Hkv + h][8] */
+    uint32_t *status;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1,
+                                        uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t &r0, uint32_t &r1,
+                                          uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float *c, uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float dec_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(kDecThreads, 2)
+decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
+                        const __grid_constant__ CUtensorMap v_map, const DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    float *comb_o = reinterpret_cast<float *>(smem);
+    float2 *comb_ml = reinterpret_cast<float2 *>(smem + 4 * 8 * 132 * 4);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kDecSmemRing);
+    uint64_t *empty = full + kDecStages;
+    uint32_t *abort_flag = reinterpret_cast<uint32_t *>(empty + kDecStages);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const q3_decode_work w = p.work[blockIdx.x];
+    const uint32_t h = blockIdx.y;
+    const uint32_t n_keys = p.ctx_lens[w.seq] + p.extra_token;
+    const uint32_t n_pages = w.page_end - w.page_begin;
+    const uint32_t n_tiles = (n_pages + kDecTilePages - 1) / kDecTilePages;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kDecStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        /* ---------------- producer ---------------- */
+        const uint32_t *pages = p.page_indices + p.page_indptr[w.seq] + w.page_begin;
+        bool alive = true;
+        for (uint32_t t = 0; t < n_tiles && alive; t++) {
+            const uint32_t stage = t % kDecStages, ph = (t / kDecStages) & 1u;
+            const uint32_t pi = t * kDecTilePages + lane;
+            const bool have = lane < kDecTilePages && pi < n_pages;
+            const uint32_t page = have ? pages[pi] : 0u;
+            for (uint32_t i = 0; i < Q3_WAIT_POLLS; i++) {
+                alive = mbar_try_wait(&empty[stage], ph ^ 1u);
+                if (alive) break;
+            }
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) {
+                if (lane == 0) atomicExch(abort_flag, 1u);
+                break;
+            }
+            const uint32_t live = min(kDecTilePages, n_pages - t * kDecTilePages);
+            if (lane == 0) mbar_arrive_expect_tx(&full[stage], live * 8192u);
+            __syncwarp();
+            if (have) {
+                const int32_t row = (int32_t)(p.pool_row_base +
+                                              (h * p.num_pages + page) * Q3_PAGE);
+                uint8_t *kd = smem + stage * kDecStageBytes + lane * 4096u;
+                uint8_t *vd = kd + kDecTilePages * 4096u;
+                tma_load_2d(kd, &k_map, 0, row, &full[stage]);
+                tma_load_2d(kd + 2048, &k_map, 64, row, &full[stage]);
+                tma_load_2d(vd, &v_map, 0, row, &full[stage]);
+                tma_load_2d(vd + 2048, &v_map, 64, row, &full[stage]);
+            }
+        }
+        __syncthreads(); /* ring drained: consumers reuse it for the combine */
+    } else {
+        /* ---------------- consumers: warp `warp` takes page `warp` of a tile ---- */
+        const uint32_t g = lane >> 2;       /* query head row 0..7 */
+        const uint32_t tq = lane & 3u;
+        /* A fragments of Q for the 8 k-steps: a0 = (row g, d 16ks+2tq..), a2 = (+8) */
+        uint32_t qa0[8], qa2[8];
+        {
+            const __half *qrow =
+                p.q2 + ((size_t)w.seq * p.n_heads + h * Q3_G + g) * Q3_D;
+#pragma unroll
+            for (uint32_t ks = 0; ks < 8; ks++) {
+                qa0[ks] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 2 * tq);
+                qa2[ks] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 8 + 2 * tq);
+            }
+        }
+        float o[16][4];
+#pragma unroll
+        for (uint32_t i = 0; i < 16; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        const float c = p.scale_log2;
+        /* ldmatrix lane addressing inside a swizzled page half:
+         *   K (non-transposed): matrix j = lane/8; key = (j/2)*8 + lane%8; chunk += j&1
+         *   V (transposed):     matrix j = lane/8; key = (j&1)*8 + lane%8; chunk += j/2 */
+        const uint32_t lm = lane >> 3, lr = lane & 7u;
+        const uint32_t k_key = (lm >> 1) * 8 + lr, k_csel = lm & 1u;
+        const uint32_t v_key = (lm & 1u) * 8 + lr, v_csel = lm >> 1;
+        bool alive = true;
+        for (uint32_t t = 0; t < n_tiles && alive; t++) {
+            const uint32_t stage = t % kDecStages, ph = (t / kDecStages) & 1u;
+            for (uint32_t i = 0; i < Q3_WAIT_POLLS; i++) {
+                alive = mbar_try_wait(&full[stage], ph);
+                if (alive || ((i & 255u) == 255u && *(volatile uint32_t *)abort_flag)) break;
+            }
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) {
+                if (lane == 0) atomicExch(abort_flag, 1u);
+                break;
+            }
+            const uint32_t pi = t * kDecTilePages + warp;
+            if (pi < n_pages) {
+                const uint32_t kbase = smem_u32(smem + stage * kDecStageBytes + warp * 4096u);
+                const uint32_t vbase = kbase + kDecTilePages * 4096u;
+                /* S = Q K^T for the 16 keys of the page */
+                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ks++) {
+                    const uint32_t chunk = (2 * ks + k_csel) & 7u;
+                    const uint32_t addr = kbase + (ks >> 2) * 2048u + k_key * 128u +
+                                          ((chunk ^ (k_key & 7u)) << 4);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(addr, b0, b1, b2, b3);
+                    mma16816(s0, qa0[ks], 0u, qa2[ks], 0u, b0, b1);
+                    mma16816(s1, qa0[ks], 0u, qa2[ks], 0u, b2, b3);
+                }
+                /* mask keys past the context, online softmax for row g */
+                const uint32_t key0 = (w.page_begin + pi) * Q3_PAGE + 2 * tq;
+                if (key0 >= n_keys) s0[0] = -INFINITY;
+                if (key0 + 1 >= n_keys) s0[1] = -INFINITY;
+                if (key0 + 8 >= n_keys) s1[0] = -INFINITY;
+                if (key0 + 9 >= n_keys) s1[1] = -INFINITY;
+                float mx = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run, mx);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                const float alpha = dec_exp2((m_run - m_use) * c);
+                const float neg = -m_use * c;
+                const float p00 = dec_exp2(fmaf(s0[0], c, neg));
+                const float p01 = dec_exp2(fmaf(s0[1], c, neg));
+                const float p10 = dec_exp2(fmaf(s1[0], c, neg));
+                const float p11 = dec_exp2(fmaf(s1[1], c, neg));
+                l_run = l_run * alpha + (p00 + p01 + p10 + p11);
+                m_run = m_new;
+                const __half2 pa = __floats2half2_rn(p00, p01);
+                const __half2 pb = __floats2half2_rn(p10, p11);
+                const uint32_t a0 = *reinterpret_cast<const uint32_t *>(&pa);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t *>(&pb);
+#pragma unroll
+                for (uint32_t nt = 0; nt < 16; nt += 2) {
+                    o[nt][0] *= alpha;
+                    o[nt][1] *= alpha;
+                    o[nt + 1][0] *= alpha;
+                    o[nt + 1][1] *= alpha;
+                    const uint32_t chunk = (nt + v_csel) & 7u;
+                    const uint32_t addr = vbase + (nt >> 3) * 2048u + v_key * 128u +
+                                          ((chunk ^ (v_key & 7u)) << 4);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_t(addr, b0, b1, b2, b3);
+                    mma16816(o[nt], a0, 0u, a2, 0u, b0, b1);
+                    mma16816(o[nt + 1], a0, 0u, a2, 0u, b2, b3);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);
+        }
+        /* per-warp partial -> shared memory (over the drained ring) */
+        __syncthreads();
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        float *wo = comb_o + (warp * 8 + g) * 132;
+#pragma unroll
+        for (uint32_t nt = 0; nt < 16; nt++) {
+            wo[nt * 8 + 2 * tq] = o[nt][0];
+            wo[nt * 8 + 2 * tq + 1] = o[nt][1];
+        }
+        if (tq == 0) comb_ml[warp * 8 + g] = make_float2(m_run, l_run);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(p.status, Q3_STATUS_WAIT_TIMEOUT);
+    if (threadIdx.x < 128) {
+        /* combine the 4 warps: thread = (row, 8 consecutive d) */
+        const uint32_t r = threadIdx.x >> 4, d0 = (threadIdx.x & 15u) * 8;
+        const float c = p.scale_log2;
+        float M = -INFINITY;
+#pragma unroll
+        for (uint32_t wi = 0; wi < 4; wi++) M = fmaxf(M, comb_ml[wi * 8 + r].x);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float den = 0.f;
+#pragma unroll
+        for (uint32_t wi = 0; wi < 4; wi++) {
+            const float2 ml = comb_ml[wi * 8 + r];
+            const float wgt = ml.x == -INFINITY ? 0.f : dec_exp2((ml.x - M) * c);
+            den += wgt * ml.y;
+            const float *src = comb_o + (wi * 8 + r) * 132 + d0;
+#pragma unroll
+            for (uint32_t i = 0; i < 8; i++) acc[i] += wgt * src[i];
+        }
+        const bool single = p.seq_work_begin[w.seq + 1] - p.seq_work_begin[w.seq] == 1;
+        if (single && p.out_fp32) {
+            const float inv = 1.0f / den;
+            float *dst = reinterpret_cast<float *>(p.out) +
+                         ((size_t)w.seq * p.n_heads + h * Q3_G + r) * Q3_D + d0;
+            *reinterpret_cast<float4 *>(dst) =
+                make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+            *reinterpret_cast<float4 *>(dst + 4) =
+                make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+        } else if (single) {
+            const float inv = 1.0f / den;
+            uint4 u;
+            __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&u);
+#pragma unroll
+            for (uint32_t i = 0; i < 4; i++)
+                hh[i] = __floats2bfloat162_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+            *reinterpret_cast<uint4 *>(
+                reinterpret_cast<__nv_bfloat16 *>(p.out) +
+                ((size_t)w.seq * p.n_heads + h * Q3_G + r) * Q3_D + d0) = u;
+        } else {
+            const size_t slot = (size_t)w.slot * p.n_kv_heads + h;
+            float *dst = p.part_o + (slot * 8 + r) * Q3_D + d0;
+            *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            if ((threadIdx.x & 15u) == 0)
+                p.part_ml[slot * 8 + r] = make_float2(M == -INFINITY ? -INFINITY : M * c, den);
+        }
+    }
+}
+
+/* One warp per (sequence, query head): combine that sequence's chunks. */
+__global__ void __launch_bounds__(256)
+decode_merge_kernel(const uint32_t *__restrict__ seq_work_begin, uint32_t num_seqs,
+                    uint32_t n_heads, uint32_t n_kv_heads,
+                    const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
+                    uint32_t out_fp32, void *__restrict__ out) {
+    const uint32_t gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (gw >= num_seqs * n_heads) return;
+    const uint32_t seq = gw / n_heads, head = gw % n_heads;
+    const uint32_t wb = seq_work_begin[seq], we = seq_work_begin[seq + 1];
+    if (we - wb <= 1) return; /* written directly by the attention kernel */
+    const uint32_t h = head / Q3_G, r = head % Q3_G;
+    float M = -INFINITY;
+    for (uint32_t i = wb; i < we; i++)
+        M = fmaxf(M, part_ml[((size_t)i * n_kv_heads + h) * 8 + r].x);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    for (uint32_t i = wb; i < we; i++) {
+        const size_t row = ((size_t)i * n_kv_heads + h) * 8 + r;
+        const float2 ml = part_ml[row];
+        const float wgt = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+        den += wgt * ml.y;
+        const float4 o = *reinterpret_cast<const float4 *>(part_o + row * Q3_D + lane * 4);
+        acc.x += wgt * o.x;
+        acc.y += wgt * o.y;
+        acc.z += wgt * o.z;
+        acc.w += wgt * o.w;
+    }
+    const float inv = 1.0f / den;
+    const size_t off = ((size_t)seq * n_heads + head) * Q3_D + lane * 4;
+    if (out_fp32) {
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + off) =
+            make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        return;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t *>(&lo);
+    u.y = *reinterpret_cast<uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(out) + off) = u;
+}
+
+}  // namespace
+
+bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer, const q3_decode_plan *plan,
+                      bool with_new_token, void *out_bf16, char *error,
+                      size_t error_len) {
+    const q3_attn_config &c = rt->cfg;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kDecSmemTotal);
+        if (e != cudaSuccess)
+            return q3_fail_cuda(error, error_len, "decode: shared memory opt-in", e);
+        attr_set = true;
+    }
+    DecodeParams p;
+    p.work = plan->work;
+    p.seq_work_begin = plan->seq_work_begin;
+    p.ctx_lens = plan->ctx_lens;
+    p.page_indptr = plan->page_indptr;
+    p.page_indices = plan->page_indices;
+    p.q2 = rt->q2;
+    p.n_heads = c.n_heads;
+    p.n_kv_heads = c.n_kv_heads;
+    p.num_pages = c.num_pages;
+    p.pool_row_base = layer * c.n_kv_heads * c.num_pages * Q3_PAGE;
+    p.pool_rows_total = c.num_layers * c.n_kv_heads * c.num_pages * Q3_PAGE;
+    p.extra_token = with_new_token ? 1u : 0u;
+    p.scale_log2 = (1.0f / sqrtf((float)Q3_D)) * 1.4426950408889634f;
+    p.out_fp32 = c.out_fp32;
+    p.out = out_bf16;
+    p.part_o = rt->dec_o;
+    p.part_ml = rt->dec_ml;
+    p.status = rt->status_dev;
+    dim3 grid(plan->n_work, c.n_kv_heads);
+    decode_attention_kernel<<<grid, kDecThreads, kDecSmemTotal, rt->stream>>>(
+        rt->k_map, rt->v_map, p);
+    Q3_LAUNCH_CHECK("decode_attention launch failed");
+    rt->n_launch++;
+    if (plan->n_work > plan->num_seqs) {
+        const uint32_t warps = plan->num_seqs * c.n_heads;
+        decode_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, rt->stream>>>(
+            plan->seq_work_begin, plan->num_seqs, c.n_heads, c.n_kv_heads, rt->dec_o,
+            rt->dec_ml, c.out_fp32, out_bf16);
+        Q3_LAUNCH_CHECK("decode_merge launch failed");
+        rt->n_launch++;
+    }
+    return true;
+}

@@ -1,0 +1,622 @@
+/* q3_attn_tc.cu - tensor-core attention over paged f16 KV for sm_100a.
+ *
+ * One kernel serves both tensor-bound cases of the path:
+ *   causal GQA prefill      (ref: attention_kernel, src/q3_forward.cu:218-290)
+ *   shared prefix + own suffix, packed branches
+ *                           (ref: attention_segmented_kernel, :418-525)
+ * The reference walks keys 0..P-1 of the prefix and then 0..lp of the row's own
+ * branch with one running maximum; this kernel streams the same keys in tiles
+ * of 128 (8 pages) with an online softmax, which is the same sum in a
+ * different order. A plain causal sequence is the special case "no shared
+ * prefix, one branch whose local position is the absolute position".
+ *
+ * Shape of the computation (per CTA, persistent over its schedule segments):
+ *   M tile   128 rows = 16 query tokens x the 8 query heads of one KV head
+ *            (GQA packing: the 8 heads share every K/V tile). Two M tiles per
+ *            CTA (32 tokens) ping-pong so one tile's softmax overlaps the
+ *            other's MMAs.
+ *   S = Q K^T   tcgen05.mma kind::f16, A = Q (smem, K-major, 128B swizzle),
+ *               B = K pages (smem, K-major), D = S in tensor memory (fp32).
+ *   softmax     one thread per row reads its S row with tcgen05.ld, keeps the
+ *               running max / sum in registers, writes P as f16 back into the
+ *               S columns (tcgen05.st).
+ *   O += P V    tcgen05.mma, A = P from tensor memory, B = V pages (smem,
+ *               MN-major), D = O in tensor memory (fp32).
+ *   K/V pages   4 KiB per page per head, fetched by TMA (two 64-column boxes,
+ *               128-byte swizzle) straight into the UMMA operand layout. No
+ *               multicast: every CTA issues its own loads from local HBM.
+ * Warp roles: 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation),
+ * 2-5 = softmax of M tile 0, 6-9 = softmax of M tile 1.
+ *
+ * Work is cut stream-K style on the host (q3_sched.h): a CTA receives
+ * segments (item, key-tile range). A segment that covers its whole item
+ * writes bf16 output; otherwise it writes un-normalised fp32 partials plus
+ * (max, sum) and merge_partials_kernel combines them with log-sum-exp.
+ *
+ * Every mbarrier wait is bounded; on expiry the thread raises a flag in shared
+ * memory, the status word is set and all roles drain and leave.
+ *
+ * Algorithmic cost: 4*128 FLOP per (query head row, visible key) pair; bytes
+ * = Q in + O out + each distinct K/V page once.
+ */
+#include "q3_internal.h"
+#include "q3_ptx.cuh"
+
+using namespace q3ptx;
+
+namespace {
+
+constexpr uint32_t kThreads = 320;
+constexpr uint32_t kNQ = 2;              /* M tiles per CTA */
+constexpr uint32_t kStages = 2;          /* K and V ring depth */
+constexpr uint32_t kMetaRing = 4;
+constexpr uint32_t kTileBytes = 32768;   /* 128 x 128 f16 */
+constexpr uint32_t kHalfBytes = 16384;   /* 128 rows x 64 f16 */
+constexpr uint32_t kPageHalfBytes = 2048;
+
+constexpr uint32_t kSmemQ = 0;
+constexpr uint32_t kSmemK = kSmemQ + kNQ * kTileBytes;
+constexpr uint32_t kSmemV = kSmemK + kStages * kTileBytes;
+constexpr uint32_t kSmemMisc = kSmemV + kStages * kTileBytes;
+constexpr uint32_t kSmemTotal = kSmemMisc + 2048 + 1024; /* + alignment slack */
+
+constexpr uint32_t kSlotInvalid = 0, kSlotShared = 1, kSlotPrivate = 2;
+constexpr uint32_t kNoTag = 0xFFFFFFFEu;
+
+/* TMEM columns */
+constexpr uint32_t kColS = 0;            /* S_q at kColS + q*128; P_q aliases its first 64 */
+constexpr uint32_t kColO = 256;          /* O_q at kColO + q*128 */
+
+/* lazy rescale threshold in log2 units (P stays <= 2^8, exact enough in f16) */
+constexpr float kTau = 8.0f;
+
+struct TileMeta {
+    uint32_t nomask;
+    uint32_t kind[8];
+    uint32_t tag[8];
+    uint32_t base[8];
+    uint32_t nvis[8];
+};
+
+struct Barriers {
+    uint64_t q_full, q_empty;
+    uint64_t k_full[kStages], k_empty[kStages];
+    uint64_t v_full[kStages], v_empty[kStages];
+    uint64_t s_full[kNQ], p_full[kNQ], o_full[kNQ];
+};
+
+struct Misc {
+    Barriers bar;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+    TileMeta meta[kMetaRing];
+};
+
+struct AttnParams {
+    const uint32_t *page_ids;
+    const q3_run *runs;
+    const q3_segment *segments;
+    const uint32_t *cta_seg_begin;
+    const uint32_t *row_tag;
+    const uint32_t *row_lp;
+    uint32_t tokens;
+    uint32_t n_heads;
+    uint32_t n_shared_pages;
+    uint32_t shared_len;
+    uint32_t num_pages;
+    uint32_t pool_row_base;     /* layer * n_kv_heads * num_pages * 16 */
+    uint32_t pool_rows_total;   /* first out-of-range row: zero-filled by TMA */
+    float scale_log2;           /* scale * log2(e) */
+    uint32_t out_fp32;
+    void *out;                  /* [tokens][n_heads][128] bf16, or fp32 */
+    float *part_o;
+    float2 *part_ml;
+    uint32_t *status;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+/* Wait on a barrier unless the CTA is aborting; on expiry raise the abort flag. */
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity,
+                                              Misc *misc) {
+    for (uint32_t i = 0; i < Q3_WAIT_POLLS; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *(volatile uint32_t *)&misc->abort_flag) return false;
+    }
+    atomicExch(&misc->abort_flag, 1u);
+    return false;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+                    const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Misc *misc = reinterpret_cast<Misc *>(smem + kSmemMisc);
+    Barriers &bar = misc->bar;
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar.q_full, 1);
+        mbar_init(&bar.q_empty, 1);
+        for (uint32_t s = 0; s < kStages; s++) {
+            mbar_init(&bar.k_full[s], 1);
+            mbar_init(&bar.k_empty[s], 1);
+            mbar_init(&bar.v_full[s], 1);
+            mbar_init(&bar.v_empty[s], 1);
+        }
+        for (uint32_t q = 0; q < kNQ; q++) {
+            mbar_init(&bar.s_full[q], 1);
+            mbar_init(&bar.p_full[q], 128);
+            mbar_init(&bar.o_full[q], 1);
+        }
+        misc->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&misc->tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = misc->tmem_base;
+
+    const uint32_t seg_begin = p.cta_seg_begin[blockIdx.x];
+    const uint32_t seg_end = p.cta_seg_begin[blockIdx.x + 1];
+
+    if (warp == 0) {
+        /* ===================== TMA producer ===================== */
+        if (lane == 0) {
+            prefetch_tmap(&q_map);
+            prefetch_tmap(&k_map);
+            prefetch_tmap(&v_map);
+        }
+        uint32_t it = 0;
+        bool alive = true;
+        for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
+            const q3_segment seg = p.segments[si];
+            /* CTA-wide row summary, for the "whole tile visible" shortcut */
+            const uint32_t tok = seg.tok0 + lane;
+            const bool tvalid = tok < p.tokens;
+            const uint32_t my_tag = tvalid ? p.row_tag[tok] : 0u;
+            const uint32_t my_lp = tvalid ? p.row_lp[tok] : 0xFFFFFFFFu;
+            const uint32_t first_tag = __shfl_sync(0xffffffffu, my_tag, 0);
+            const bool uniform =
+                __all_sync(0xffffffffu, !tvalid || my_tag == first_tag);
+            uint32_t min_lp = my_lp;
+            for (uint32_t o = 16; o; o >>= 1)
+                min_lp = min(min_lp, __shfl_xor_sync(0xffffffffu, min_lp, o));
+
+            if (si != seg_begin)
+                alive = wait_or_abort(&bar.q_empty, (si - seg_begin - 1) & 1u, misc);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&bar.q_full, kNQ * kTileBytes);
+                for (uint32_t q = 0; q < kNQ; q++)
+                    for (uint32_t half = 0; half < 2; half++)
+                        tma_load_3d(smem + kSmemQ + q * kTileBytes + half * kHalfBytes,
+                                    &q_map, (int32_t)(half * 64),
+                                    (int32_t)(seg.kv_head * Q3_G),
+                                    (int32_t)(seg.tok0 + q * 16), &bar.q_full);
+            }
+            for (uint32_t tile = seg.tile_begin; tile < seg.tile_end; tile++, it++) {
+                const uint32_t stage = it % kStages;
+                const uint32_t ph = (it / kStages) & 1u;
+                /* lanes 0..7 resolve one page slot each */
+                uint32_t kind = kSlotInvalid, tag = 0, base = 0, nvis = 0;
+                uint32_t page = 0;
+                if (lane < 8) {
+                    if (tile < seg.shared_tiles) {
+                        const uint32_t pidx = tile * 8 + lane;
+                        if (pidx < p.n_shared_pages) {
+                            page = p.page_ids[pidx];
+                            kind = kSlotShared;
+                            nvis = min(16u, p.shared_len - pidx * 16u);
+                        }
+                    } else {
+                        uint32_t f = (tile - seg.shared_tiles) * 8 + lane;
+                        for (uint32_t r = seg.run_begin; r < seg.run_end; r++) {
+                            const q3_run run = p.runs[r];
+                            if (f < run.n_pages) {
+                                page = p.page_ids[run.table_off + f];
+                                kind = kSlotPrivate;
+                                tag = run.tag;
+                                base = f * 16u;
+                                break;
+                            }
+                            f -= run.n_pages;
+                        }
+                    }
+                }
+                const bool whole =
+                    (kind == kSlotShared && nvis == 16u) ||
+                    (kind == kSlotPrivate && uniform && tag == first_tag &&
+                     base + 15u <= min_lp);
+                const uint32_t whole_mask = __ballot_sync(0xffffffffu, whole) & 0xFFu;
+                const int32_t row =
+                    kind == kSlotInvalid
+                        ? (int32_t)p.pool_rows_total
+                        : (int32_t)(p.pool_row_base +
+                                    (seg.kv_head * p.num_pages + page) * Q3_PAGE);
+
+                alive = wait_or_abort(&bar.k_empty[stage], ph ^ 1u, misc);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                TileMeta &m = misc->meta[it % kMetaRing];
+                if (lane < 8) {
+                    m.kind[lane] = kind;
+                    m.tag[lane] = tag;
+                    m.base[lane] = base;
+                    m.nvis[lane] = nvis;
+                }
+                if (lane == 0) {
+                    m.nomask = whole_mask == 0xFFu;
+                    mbar_arrive_expect_tx(&bar.k_full[stage], kTileBytes);
+                }
+                __syncwarp();
+                if (lane < 8) {
+                    uint8_t *dst = smem + kSmemK + stage * kTileBytes + lane * kPageHalfBytes;
+                    tma_load_2d(dst, &k_map, 0, row, &bar.k_full[stage]);
+                    tma_load_2d(dst + kHalfBytes, &k_map, 64, row, &bar.k_full[stage]);
+                }
+                alive = wait_or_abort(&bar.v_empty[stage], ph ^ 1u, misc);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                if (lane == 0) mbar_arrive_expect_tx(&bar.v_full[stage], kTileBytes);
+                __syncwarp();
+                if (lane < 8) {
+                    uint8_t *dst = smem + kSmemV + stage * kTileBytes + lane * kPageHalfBytes;
+                    tma_load_2d(dst, &v_map, 0, row, &bar.v_full[stage]);
+                    tma_load_2d(dst + kHalfBytes, &v_map, 64, row, &bar.v_full[stage]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        /* ===================== MMA issuer ======================= */
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = umma_idesc_f16(128, 128, false);
+            constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, true);
+            const uint32_t q_addr = smem_u32(smem + kSmemQ);
+            const uint32_t k_addr = smem_u32(smem + kSmemK);
+            const uint32_t v_addr = smem_u32(smem + kSmemV);
+            uint32_t it = 0;
+            bool alive = true;
+
+            auto issue_s = [&](uint32_t q, uint32_t stage) {
+                /* S_q = Q_q K^T : 8 steps of K = 16 over head_dim = 128 */
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ks++) {
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3u) * 32u;
+                    umma_ss(tmem + kColS + q * 128u,
+                            umma_desc(q_addr + q * kTileBytes + off, 16, 1024),
+                            umma_desc(k_addr + stage * kTileBytes + off, 16, 1024),
+                            idesc_qk, ks > 0);
+                }
+                umma_commit(&bar.s_full[q]);
+            };
+            auto issue_pv = [&](uint32_t q, uint32_t stage, bool accumulate) {
+                /* O_q += P_q V : 8 steps of K = 16 keys; V is MN-major
+                 * (64-column blocks 16 KiB apart, 8-key groups 1 KiB apart) */
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ks++)
+                    umma_ts(tmem + kColO + q * 128u, tmem + kColS + q * 128u + ks * 8u,
+                            umma_desc(v_addr + stage * kTileBytes + ks * 2048u, kHalfBytes,
+                                      1024),
+                            idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+                umma_commit(&bar.o_full[q]);
+            };
+
+            for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
+                const q3_segment seg = p.segments[si];
+                const uint32_t n = seg.tile_end - seg.tile_begin;
+                alive = wait_or_abort(&bar.q_full, (si - seg_begin) & 1u, misc);
+                if (!alive) break;
+                /* S of the segment's first tile */
+                {
+                    const uint32_t stage = it % kStages;
+                    alive = wait_or_abort(&bar.k_full[stage], (it / kStages) & 1u, misc);
+                    if (!alive) break;
+                    tc_fence_after();
+                    issue_s(0, stage);
+                    issue_s(1, stage);
+                    umma_commit(&bar.k_empty[stage]);
+                    if (n == 1) umma_commit(&bar.q_empty);
+                }
+                for (uint32_t j = 0; j < n && alive; j++, it++) {
+                    const uint32_t stage = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    const uint32_t nstage = (it + 1) % kStages;
+                    const uint32_t nph = ((it + 1) / kStages) & 1u;
+                    const bool more = j + 1 < n;
+                    for (uint32_t q = 0; q < kNQ && alive; q++) {
+                        alive = wait_or_abort(&bar.p_full[q], it & 1u, misc);
+                        if (alive && q == 0)
+                            alive = wait_or_abort(&bar.v_full[stage], ph, misc);
+                        if (!alive) break;
+                        tc_fence_after();
+                        issue_pv(q, stage, j > 0);
+                        if (q == kNQ - 1) umma_commit(&bar.v_empty[stage]);
+                        if (more) {
+                            if (q == 0) {
+                                alive = wait_or_abort(&bar.k_full[nstage], nph, misc);
+                                if (!alive) break;
+                                tc_fence_after();
+                            }
+                            issue_s(q, nstage);
+                            if (q == kNQ - 1) {
+                                umma_commit(&bar.k_empty[nstage]);
+                                if (j + 2 == n) umma_commit(&bar.q_empty);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        /* ===================== softmax groups ==================== */
+        const uint32_t q = (warp - 2) >> 2;                 /* M tile of this group */
+        const uint32_t row = (warp & 3u) * 32u + lane;       /* TMEM lane == tile row */
+        const uint32_t lane_addr = ((warp & 3u) * 32u) << 16;
+        const uint32_t s_addr = tmem + lane_addr + kColS + q * 128u;
+        const uint32_t o_addr = tmem + lane_addr + kColO + q * 128u;
+        const float c = p.scale_log2;
+        const float tau_raw = kTau / c;
+        uint32_t it = 0;
+        bool alive = true;
+
+        for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
+            const q3_segment seg = p.segments[si];
+            const uint32_t n = seg.tile_end - seg.tile_begin;
+            const uint32_t token = seg.tok0 + q * 16u + (row >> 3);
+            const uint32_t head = seg.kv_head * Q3_G + (row & 7u);
+            const bool valid = token < p.tokens;
+            const uint32_t tag_r = valid ? p.row_tag[token] : kNoTag;
+            const uint32_t lp_r = valid ? p.row_lp[token] : 0u;
+            float m_ref = -INFINITY, l = 0.f;
+
+            for (uint32_t j = 0; j < n && alive; j++, it++) {
+                alive = wait_or_abort(&bar.s_full[q], it & 1u, misc);
+                if (alive && j > 0)
+                    alive = wait_or_abort(&bar.o_full[q], (it - 1) & 1u, misc);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                tc_fence_after();
+                float s[128];
+#pragma unroll
+                for (uint32_t ch = 0; ch < 4; ch++)
+                    tmem_ld32(s_addr + ch * 32u, reinterpret_cast<uint32_t *>(s) + ch * 32u);
+                tmem_wait_ld();
+                const TileMeta &m = misc->meta[it % kMetaRing];
+                if (!m.nomask) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; i++) {
+                        const uint32_t kind = m.kind[i];
+                        uint32_t nvis = 0;
+                        if (kind == kSlotShared) {
+                            nvis = m.nvis[i];
+                        } else if (kind == kSlotPrivate && m.tag[i] == tag_r) {
+                            const uint32_t b = m.base[i];
+                            nvis = lp_r >= b ? min(16u, lp_r - b + 1u) : 0u;
+                        }
+#pragma unroll
+                        for (uint32_t k2 = 0; k2 < 16; k2++)
+                            if (k2 >= nvis) s[i * 16 + k2] = -INFINITY;
+                    }
+                }
+                float mx = s[0];
+#pragma unroll
+                for (uint32_t i = 1; i < 128; i++) mx = fmaxf(mx, s[i]);
+
+                if (j == 0) {
+                    m_ref = mx;
+                } else {
+                    const bool need = mx > m_ref + tau_raw;
+                    if (__any_sync(0xffffffffu, need)) {
+                        /* O_q was last written by PV(j-1), complete (o_full). */
+                        const float f = need ? fast_exp2((m_ref - mx) * c) : 1.0f;
+                        if (need) m_ref = mx;
+                        l *= f;
+#pragma unroll
+                        for (uint32_t ch = 0; ch < 4; ch++) {
+                            uint32_t o[32];
+                            tmem_ld32(o_addr + ch * 32u, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (uint32_t i = 0; i < 32; i++)
+                                o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                            tmem_st32(o_addr + ch * 32u, o);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                const float neg = (m_ref == -INFINITY) ? 0.f : -m_ref * c;
+                uint32_t pk[64];
+                float sum = 0.f;
+#pragma unroll
+                for (uint32_t i = 0; i < 64; i++) {
+                    const float p0 = fast_exp2(fmaf(s[2 * i], c, neg));
+                    const float p1 = fast_exp2(fmaf(s[2 * i + 1], c, neg));
+                    sum += p0 + p1;
+                    const __half2 h = __floats2half2_rn(p0, p1);
+                    pk[i] = *reinterpret_cast<const uint32_t *>(&h);
+                }
+                l += sum;
+                tmem_st32(s_addr, pk);
+                tmem_st32(s_addr + 32u, pk + 32);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&bar.p_full[q]);
+            }
+            if (!alive) break;
+            /* ---- segment epilogue: O_q of the last tile ---- */
+            alive = wait_or_abort(&bar.o_full[q], (it - 1) & 1u, misc);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            tc_fence_after();
+            if (seg.partial_slot < 0) {
+                const float inv = 1.0f / l;
+                const size_t orow = ((size_t)token * p.n_heads + head) * Q3_D;
+                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.out) + orow;
+                float *dst32 = reinterpret_cast<float *>(p.out) + orow;
+#pragma unroll
+                for (uint32_t ch = 0; ch < 4; ch++) {
+                    uint32_t o[32];
+                    tmem_ld32(o_addr + ch * 32u, o);
+                    tmem_wait_ld();
+                    if (valid && p.out_fp32) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; i++)
+                            *reinterpret_cast<float4 *>(dst32 + ch * 32 + i * 4) = make_float4(
+                                __uint_as_float(o[i * 4]) * inv,
+                                __uint_as_float(o[i * 4 + 1]) * inv,
+                                __uint_as_float(o[i * 4 + 2]) * inv,
+                                __uint_as_float(o[i * 4 + 3]) * inv);
+                    } else if (valid) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; i++) {
+                            uint4 u;
+                            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&u);
+#pragma unroll
+                            for (uint32_t e = 0; e < 4; e++)
+                                h[e] = __floats2bfloat162_rn(
+                                    __uint_as_float(o[i * 8 + 2 * e]) * inv,
+                                    __uint_as_float(o[i * 8 + 2 * e + 1]) * inv);
+                            *reinterpret_cast<uint4 *>(dst + ch * 32 + i * 8) = u;
+                        }
+                    }
+                }
+            } else {
+                const size_t prow = (size_t)seg.partial_slot * 256 + q * 128 + row;
+                float *dst = p.part_o + prow * Q3_D;
+#pragma unroll
+                for (uint32_t ch = 0; ch < 4; ch++) {
+                    uint32_t o[32];
+                    tmem_ld32(o_addr + ch * 32u, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; i++)
+                        *reinterpret_cast<uint4 *>(dst + ch * 32 + i * 4) =
+                            make_uint4(o[i * 4], o[i * 4 + 1], o[i * 4 + 2], o[i * 4 + 3]);
+                }
+                p.part_ml[prow] =
+                    make_float2(m_ref == -INFINITY ? -INFINITY : m_ref * c, l);
+            }
+            /* the next segment's first PV overwrites O_q only after p_full of
+             * its first tile, which this thread raises after these loads */
+            tc_fence_before();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && misc->abort_flag) atomicOr(p.status, Q3_STATUS_WAIT_TIMEOUT);
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+/* Combine the partials of items that were cut across CTAs:
+ *   M = max_i m_i;  out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i
+ * which equals the single-pass result (ref: one running max over both
+ * segments, src/q3_forward.cu:452-518) up to rounding. One warp per row. */
+__global__ void __launch_bounds__(256)
+merge_partials_kernel(const q3_merge_item *__restrict__ merges,
+                      const float *__restrict__ part_o,
+                      const float2 *__restrict__ part_ml, uint32_t tokens,
+                      uint32_t n_heads, uint32_t out_fp32, void *__restrict__ out) {
+    const q3_merge_item mi = merges[blockIdx.x];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    for (uint32_t r = blockIdx.y * 8 + warp; r < 256; r += gridDim.y * 8) {
+        const uint32_t token = mi.tok0 + (r >> 7) * 16u + ((r & 127u) >> 3);
+        if (token >= tokens) continue;
+        const uint32_t head = mi.kv_head * Q3_G + (r & 7u);
+        float M = -INFINITY;
+        for (uint32_t i = 0; i < mi.slot_count; i++)
+            M = fmaxf(M, part_ml[(size_t)(mi.slot_begin + i) * 256 + r].x);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float den = 0.f;
+        for (uint32_t i = 0; i < mi.slot_count; i++) {
+            const size_t prow = (size_t)(mi.slot_begin + i) * 256 + r;
+            const float2 ml = part_ml[prow];
+            const float w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
+            den += w * ml.y;
+            const float4 o = *reinterpret_cast<const float4 *>(part_o + prow * Q3_D + lane * 4);
+            acc.x += w * o.x;
+            acc.y += w * o.y;
+            acc.z += w * o.z;
+            acc.w += w * o.w;
+        }
+        const float inv = 1.0f / den;
+        const size_t off = ((size_t)token * n_heads + head) * Q3_D + lane * 4;
+        if (out_fp32) {
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + off) =
+                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+            uint2 u;
+            u.x = *reinterpret_cast<uint32_t *>(&lo);
+            u.y = *reinterpret_cast<uint32_t *>(&hi);
+            *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(out) + off) = u;
+        }
+    }
+}
+
+}  // namespace
+
+bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st,
+                         void *out_bf16, char *error, size_t error_len) {
+    const q3_attn_config &c = rt->cfg;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemTotal);
+        if (e != cudaSuccess)
+            return q3_fail_cuda(error, error_len, "attention_tc: shared memory opt-in", e);
+        attr_set = true;
+    }
+    CUtensorMap q_map;
+    if (!q3_encode_tmap_q(&q_map, rt->q2, c.n_heads, st->tokens, error, error_len))
+        return false;
+    AttnParams p;
+    p.page_ids = st->page_ids;
+    p.runs = st->runs;
+    p.segments = st->segments;
+    p.cta_seg_begin = st->cta_seg_begin;
+    p.row_tag = st->row_tag;
+    p.row_lp = st->row_lp;
+    p.tokens = st->tokens;
+    p.n_heads = c.n_heads;
+    p.n_shared_pages = st->n_shared_pages;
+    p.shared_len = st->shared_len;
+    p.num_pages = c.num_pages;
+    p.pool_row_base = layer * c.n_kv_heads * c.num_pages * Q3_PAGE;
+    p.pool_rows_total = c.num_layers * c.n_kv_heads * c.num_pages * Q3_PAGE;
+    p.scale_log2 = (1.0f / sqrtf((float)Q3_D)) * 1.4426950408889634f;
+    p.out_fp32 = c.out_fp32;
+    p.out = out_bf16;
+    p.part_o = rt->part_o;
+    p.part_ml = rt->part_ml;
+    p.status = rt->status_dev;
+    attention_tc_kernel<<<st->grid, kThreads, kSmemTotal, rt->stream>>>(q_map, rt->k_map,
+                                                                       rt->v_map, p);
+    Q3_LAUNCH_CHECK("attention_tc launch failed");
+    rt->n_launch++;
+    if (st->n_merges) {
+        dim3 grid(st->n_merges, 8);
+        merge_partials_kernel<<<grid, 256, 0, rt->stream>>>(
+            st->merges, rt->part_o, rt->part_ml, st->tokens, c.n_heads, c.out_fp32,
+            out_bf16);
+        Q3_LAUNCH_CHECK("merge_partials launch failed");
+        rt->n_launch++;
+    }
+    return true;
+}

@@ -1,0 +1,188 @@
+/* q3_internal.h - private structs shared by the translation units of
+ * libq3attn. Nothing here is part of the C ABI (include/q3_attn.h is). */
+#ifndef Q3_INTERNAL_H
+#define Q3_INTERNAL_H
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <vector>
+
+#include "q3_attn.h"
+#include "q3_sched.h"
+
+#define Q3_D 128u          /* head_dim the kernels are specialised for     */
+#define Q3_G 8u            /* query heads per KV head                       */
+#define Q3_PAGE 16u        /* tokens per KV page                            */
+
+/* device_status bits (set by kernels whose bounded waits gave up) */
+#define Q3_STATUS_WAIT_TIMEOUT 1u
+
+static inline void q3_clear_error(char *error, size_t error_len) {
+    if (error && error_len) error[0] = '\0';
+}
+
+static inline bool q3_fail(char *error, size_t error_len, const char *msg) {
+    if (error && error_len) {
+        error[0] = '\0';
+        snprintf(error, error_len, "%s", msg);
+    }
+    return false;
+}
+
+static inline bool q3_fail_cuda(char *error, size_t error_len, const char *what,
+                                cudaError_t code) {
+    if (error && error_len) {
+        error[0] = '\0';
+        snprintf(error, error_len, "%s: %s", what, cudaGetErrorString(code));
+    }
+    return false;
+}
+
+/* Read the launch status right after a launch, as the reference does
+ * (ref: src/q3_forward.cu:632-636). */
+#define Q3_LAUNCH_CHECK(what)                                             \
+    do {                                                                  \
+        cudaError_t q3_code_ = cudaGetLastError();                        \
+        if (q3_code_ != cudaSuccess)                                      \
+            return q3_fail_cuda(error, error_len, (what), q3_code_);      \
+    } while (0)
+
+struct q3_attn_runtime {
+    q3_attn_config cfg;
+    cudaStream_t stream;
+    int num_sms;
+
+    __half *k_pool;   /* [L][Hkv][num_pages][16][128] */
+    __half *v_pool;
+    CUtensorMap k_map; /* 2-D {128, L*Hkv*num_pages*16}, box {64,16}, SW128 */
+    CUtensorMap v_map;
+    std::vector<uint32_t> free_pages;
+
+    float *qk_norm_w;  /* device [L][2][128] */
+    float2 *rope_table; /* device [max_positions][64] (cos, sin) */
+    __half *q2;        /* workspace [max_tokens][n_heads][128] */
+
+    /* stream-K partial accumulators, sized for 2 slots per SM */
+    float *part_o;     /* [slots][256][128] */
+    float2 *part_ml;   /* [slots][256] (max in log2 units, sum) */
+    uint32_t part_slots;
+
+    /* decode split partials */
+    float *dec_o;      /* [dec_slots][8][128] */
+    float2 *dec_ml;    /* [dec_slots][8] */
+    uint32_t dec_slots;
+
+    uint32_t *status_dev;
+    uint32_t *status_host; /* pinned mirror, refreshed by q3_attn_synchronize */
+
+    /* pinned staging for the host-buffer entry point (grow-once) */
+    void *host_stage;
+    size_t host_stage_bytes;
+    void *dev_stage;
+    size_t dev_stage_bytes;
+
+    uint64_t n_alloc, n_free, n_sync, n_launch;
+    uint64_t workspace_bytes;
+};
+
+struct q3_prefix_kv {
+    q3_attn_runtime *rt;
+    uint32_t capacity;
+    uint32_t token_count;
+    bool sealed;
+    bool owns_pages;
+    std::vector<uint32_t> pages; /* ceil(capacity/16) physical page ids */
+    /* staged descriptors for prefill chunks (grow-once, device + pinned) */
+    struct q3_stage *stage;
+};
+
+struct q3_branch_set {
+    q3_prefix_kv *prefix;
+    uint32_t max_branches;
+    uint32_t max_suffix;
+    uint32_t pages_per_branch;
+    uint32_t live;
+    std::vector<uint8_t> in_use;
+    std::vector<uint32_t> pages; /* [max_branches][pages_per_branch] */
+};
+
+/* Device-resident descriptors + schedule of one attention launch. */
+struct q3_stage {
+    q3_attn_runtime *rt;
+    void *host;        /* pinned */
+    void *dev;
+    size_t bytes;      /* capacity of both */
+    /* device views into `dev`, valid after q3_stage_upload */
+    const uint32_t *rope_pos, *dst_page, *dst_slot;
+    const uint32_t *row_tag, *row_lp;
+    const uint32_t *page_ids;
+    const uint32_t *tile_run_begin;
+    const q3_run *runs;
+    const q3_segment *segments;
+    const uint32_t *cta_seg_begin;
+    const q3_merge_item *merges;
+    uint32_t tokens, n_shared_pages, shared_len, grid, n_merges;
+    /* prefill chunks: which (base, tokens) the staged schedule describes */
+    bool chunk_valid;
+    uint32_t chunk_base, chunk_tokens;
+};
+
+struct q3_pack_plan {
+    q3_prefix_kv *prefix;
+    q3_branch_set *set;
+    uint32_t tokens, branches;
+    std::vector<uint32_t> token_positions, token_branch, token_local_pos,
+        branch_offsets;
+    q3_stage *stage;
+};
+
+struct q3_decode_plan {
+    q3_attn_runtime *rt;
+    uint32_t num_seqs;
+    uint32_t n_work;     /* (sequence, chunk) work items per KV head */
+    uint32_t chunk_pages;
+    bool can_append;     /* every sequence has a page slot for one more token */
+    void *dev;
+    const uint32_t *ctx_lens, *page_indptr, *page_indices;
+    const uint32_t *rope_pos, *dst_page, *dst_slot;
+    const q3_decode_work *work;
+    const uint32_t *seq_work_begin; /* [num_seqs+1] */
+};
+
+/* --- cross-file helpers ------------------------------------------------- */
+q3_stage *q3_stage_create(q3_attn_runtime *rt, char *error, size_t error_len);
+void q3_stage_destroy(q3_stage *st);
+/* Serialise a host schedule into the stage's pinned buffer and queue the copy
+ * on the runtime's stream. Grows the buffers when needed (counted). */
+bool q3_stage_upload(q3_stage *st, const q3_schedule &sched,
+                     const std::vector<uint32_t> &rope_pos,
+                     const std::vector<uint32_t> &dst_page,
+                     const std::vector<uint32_t> &dst_slot,
+                     char *error, size_t error_len);
+
+bool q3_launch_kvwrite(q3_attn_runtime *rt, uint32_t layer, const void *q,
+                       const void *k, const void *v, uint32_t tokens,
+                       const uint32_t *rope_pos, const uint32_t *dst_page,
+                       const uint32_t *dst_slot, void *q_out, char *error,
+                       size_t error_len);
+bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer,
+                         const q3_stage *st, void *out_bf16, char *error,
+                         size_t error_len);
+bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer,
+                      const q3_decode_plan *plan, bool with_new_token,
+                      void *out_bf16, char *error, size_t error_len);
+
+bool q3_encode_tmap_2d(CUtensorMap *map, const void *base, uint64_t inner,
+                       uint64_t rows, uint32_t box_inner, uint32_t box_rows,
+                       char *error, size_t error_len);
+bool q3_encode_tmap_q(CUtensorMap *map, const void *base, uint32_t n_heads,
+                      uint32_t tokens, char *error, size_t error_len);
+
+#endif /* Q3_INTERNAL_H */

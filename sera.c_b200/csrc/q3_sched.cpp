@@ -1,0 +1,165 @@
+/* q3_sched.cpp - see q3_sched.h. Pure host code, no CUDA. */
+#include "q3_sched.h"
+
+#include <stdio.h>
+
+#include <algorithm>
+
+static bool sched_fail(char *error, size_t error_len, const char *msg) {
+    if (error && error_len) snprintf(error, error_len, "%s", msg);
+    return false;
+}
+
+bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
+                       uint32_t shared_len,
+                       const std::vector<uint32_t> &shared_pages,
+                       const uint32_t *row_tag, const uint32_t *row_lp,
+                       const std::vector<uint32_t> &private_table,
+                       uint32_t private_stride, uint32_t num_ctas,
+                       uint32_t max_slots, char *error, size_t error_len) {
+    s = q3_schedule();
+    if (tokens == 0 || n_kv_heads == 0 || num_ctas == 0)
+        return sched_fail(error, error_len, "schedule: empty launch");
+    const uint32_t n_shared_pages = (shared_len + 15u) / 16u;
+    if (shared_pages.size() < n_shared_pages)
+        return sched_fail(error, error_len, "schedule: shared page table too short");
+    s.tokens = tokens;
+    s.n_kv_heads = n_kv_heads;
+    s.shared_len = shared_len;
+    s.n_shared_pages = n_shared_pages;
+    s.page_ids.assign(shared_pages.begin(), shared_pages.begin() + n_shared_pages);
+    s.page_ids.insert(s.page_ids.end(), private_table.begin(), private_table.end());
+    s.row_tag.assign(row_tag, row_tag + tokens);
+    s.row_lp.assign(row_lp, row_lp + tokens);
+
+    /* Runs: distinct branches of each token tile, in order of first
+     * appearance, each with the pages its rows can see. */
+    const uint32_t n_tok_tiles = (tokens + Q3_TOK_TILE - 1) / Q3_TOK_TILE;
+    s.tile_run_begin.resize(n_tok_tiles + 1);
+    std::vector<uint32_t> tile_private_pages(n_tok_tiles);
+    for (uint32_t tt = 0; tt < n_tok_tiles; tt++) {
+        s.tile_run_begin[tt] = (uint32_t)s.runs.size();
+        const uint32_t t0 = tt * Q3_TOK_TILE;
+        const uint32_t t1 = std::min(tokens, t0 + Q3_TOK_TILE);
+        const size_t first = s.runs.size();
+        for (uint32_t t = t0; t < t1; t++) {
+            const uint32_t need = row_lp[t] / 16u + 1u;
+            size_t r = first;
+            for (; r < s.runs.size(); r++)
+                if (s.runs[r].tag == row_tag[t]) break;
+            if (r == s.runs.size()) {
+                if (need > private_stride ||
+                    (uint64_t)row_tag[t] * private_stride + private_stride >
+                        private_table.size())
+                    return sched_fail(error, error_len,
+                                      "schedule: private page table too short");
+                q3_run run;
+                run.table_off = n_shared_pages + row_tag[t] * private_stride;
+                run.n_pages = need;
+                run.tag = row_tag[t];
+                run.pad = 0;
+                s.runs.push_back(run);
+            } else if (need > s.runs[r].n_pages) {
+                if (need > private_stride)
+                    return sched_fail(error, error_len,
+                                      "schedule: private page table too short");
+                s.runs[r].n_pages = need;
+            }
+        }
+        uint32_t pages = 0;
+        for (size_t r = first; r < s.runs.size(); r++) pages += s.runs[r].n_pages;
+        tile_private_pages[tt] = pages;
+    }
+    s.tile_run_begin[n_tok_tiles] = (uint32_t)s.runs.size();
+
+    /* Items in (kv_head, token tile) order and their key-tile counts. */
+    const uint32_t shared_tiles =
+        (n_shared_pages + Q3_KEY_TILE_PAGES - 1) / Q3_KEY_TILE_PAGES;
+    uint64_t total = 0;
+    std::vector<uint32_t> item_tiles(n_tok_tiles);
+    for (uint32_t tt = 0; tt < n_tok_tiles; tt++) {
+        item_tiles[tt] = shared_tiles + (tile_private_pages[tt] + Q3_KEY_TILE_PAGES - 1) /
+                                            Q3_KEY_TILE_PAGES;
+        total += item_tiles[tt];
+    }
+    total *= n_kv_heads;
+    s.total_key_tiles = total;
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(num_ctas, total);
+    s.grid = grid;
+    s.cta_seg_begin.assign(grid + 1, 0);
+
+    /* Stream-K cut: CTA c owns global key tiles [c*total/grid, (c+1)*total/grid). */
+    uint64_t pos = 0; /* global key-tile cursor */
+    uint32_t cta = 0;
+    uint64_t cta_end = total / grid; /* end of CTA 0 */
+    for (uint32_t h = 0; h < n_kv_heads; h++) {
+        for (uint32_t tt = 0; tt < n_tok_tiles; tt++) {
+            const uint32_t n = item_tiles[tt];
+            uint32_t done = 0;
+            const size_t first_seg = s.segments.size();
+            while (done < n) {
+                while (pos >= cta_end && cta + 1 < grid) {
+                    cta++;
+                    s.cta_seg_begin[cta] = (uint32_t)s.segments.size();
+                    cta_end = (uint64_t)(cta + 1) * total / grid;
+                }
+                const uint32_t take =
+                    (uint32_t)std::min<uint64_t>(n - done, cta_end - pos);
+                q3_segment seg;
+                seg.tok0 = tt * Q3_TOK_TILE;
+                seg.kv_head = h;
+                seg.tile_begin = done;
+                seg.tile_end = done + take;
+                seg.shared_tiles = shared_tiles;
+                seg.partial_slot = -1;
+                seg.run_begin = s.tile_run_begin[tt];
+                seg.run_end = s.tile_run_begin[tt + 1];
+                s.segments.push_back(seg);
+                done += take;
+                pos += take;
+            }
+            const uint32_t n_seg = (uint32_t)(s.segments.size() - first_seg);
+            if (n_seg > 1) {
+                if (s.n_slots + n_seg > max_slots)
+                    return sched_fail(error, error_len,
+                                      "schedule: out of partial slots");
+                q3_merge_item m;
+                m.tok0 = tt * Q3_TOK_TILE;
+                m.kv_head = h;
+                m.slot_begin = s.n_slots;
+                m.slot_count = n_seg;
+                for (uint32_t i = 0; i < n_seg; i++)
+                    s.segments[first_seg + i].partial_slot = (int32_t)(s.n_slots + i);
+                s.n_slots += n_seg;
+                s.merges.push_back(m);
+            }
+        }
+    }
+    for (uint32_t c = cta + 1; c <= grid; c++)
+        s.cta_seg_begin[c] = (uint32_t)s.segments.size();
+    return true;
+}
+
+void q3_build_decode_work(const uint32_t *ctx_lens, uint32_t num_seqs,
+                          uint32_t extra_token, uint32_t chunk_pages,
+                          std::vector<q3_decode_work> &work,
+                          std::vector<uint32_t> &seq_work_begin) {
+    work.clear();
+    seq_work_begin.assign(num_seqs + 1, 0);
+    for (uint32_t sidx = 0; sidx < num_seqs; sidx++) {
+        seq_work_begin[sidx] = (uint32_t)work.size();
+        const uint32_t keys = ctx_lens[sidx] + extra_token;
+        const uint32_t pages = (keys + 15u) / 16u;
+        /* equal-size chunks, none longer than chunk_pages */
+        const uint32_t n_chunks = std::max(1u, (pages + chunk_pages - 1) / chunk_pages);
+        for (uint32_t c = 0; c < n_chunks; c++) {
+            q3_decode_work w;
+            w.seq = sidx;
+            w.page_begin = (uint32_t)((uint64_t)c * pages / n_chunks);
+            w.page_end = (uint32_t)((uint64_t)(c + 1) * pages / n_chunks);
+            w.slot = (uint32_t)work.size();
+            work.push_back(w);
+        }
+    }
+    seq_work_begin[num_seqs] = (uint32_t)work.size();
+}
