@@ -1,0 +1,498 @@
+"""Benchmark of the attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N \
+        --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+Workload ("stack64_p32768_b128x16"): the 64-layer attention stack of the
+Qwen3-32B forward over a shared prefix of 32768 tokens resident in paged f16 KV
+plus 128 branches x 16 packed suffix tokens (2048 query tokens), Q/K/V per layer
+seeded bf16 N(0,1) (seed = layer index). One step = all 64 layers: fused
+QK-RMSNorm + RoPE + KV write of the suffix tokens, then shared-prefix +
+own-suffix attention. With N GPUs the KV heads are sharded (8/N KV heads and
+their 64/N query heads per rank) and the per-head outputs are all-gathered
+after every layer (NCCL, overlapped with the next layer).
+
+value      suffix tokens per second through the 64-layer stack, inputs resident
+           in HBM, device-timed (CUDA events on the launching stream), max over
+           ranks.
+e2e        the same through the host-buffer C-ABI entry: per layer, q/k/v come
+           from pinned host memory and the output goes back to pinned host
+           memory, copies inside the timed region.
+roofline   the tensor-core attention kernel: algorithmic FLOPs per launch
+           (4*128 per query-head row and visible key) / its mean device time,
+           against the measured bf16 peak of MEASURED_PEAKS.json.
+cpu_baseline  the CPU oracle (OpenMP, all host threads) on a bounded sample of
+           the same workload.
+Synthetic data throughout; there is no dataset for this path.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, HKV, D, L = 64, 8, 128, 64
+PREFIX, BRANCHES, SUFFIX = 32768, 128, 16
+TOKENS = BRANCHES * SUFFIX
+WORKLOAD = "stack64_p32768_b128x16"
+METRIC = "attn_suffix_tokens_per_s"
+UNIT = "tokens/s"
+# visible (query-head row, key) pairs per layer * 4*D FLOPs
+PAIRS_PER_HEAD = TOKENS * PREFIX + BRANCHES * (SUFFIX * (SUFFIX + 1) // 2)
+FLOPS_PER_LAYER = 4 * D * H * PAIRS_PER_HEAD
+FLOPS_PER_STEP = FLOPS_PER_LAYER * L
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tflops_burst=p["bf16_tflops"],
+                    tflops_sustained=p["bf16_tflops_sustained"], source="measured")
+    except Exception:
+        return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0,
+                    source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU during a timed region."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None,
+                    sm_max_mhz=float(max(mx)) if mx else None,
+                    samples=len(sm), reasons=sorted(reasons))
+
+
+def shard_inputs(torch, layer, rank, n_gpus, device):
+    """Seeded bf16 N(0,1) q/k/v of one layer, sliced to this rank's heads."""
+    g = torch.Generator(device="cpu").manual_seed(layer)
+    q = torch.randn(TOKENS, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(TOKENS, HKV, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(TOKENS, HKV, D, generator=g).to(torch.bfloat16)
+    hq, hk = H // n_gpus, HKV // n_gpus
+    return (q[:, rank * hq:(rank + 1) * hq].contiguous(),
+            k[:, rank * hk:(rank + 1) * hk].contiguous(),
+            v[:, rank * hk:(rank + 1) * hk].contiguous())
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    n_gpus = args.gpus
+    if world != n_gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run"
+                         % (n_gpus, world))
+    if HKV % n_gpus:
+        raise SystemExit("KV-head sharding needs --gpus in {1,2,4,8}")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    entry.build()
+    pkg = entry.load_package()
+    hq, hk = H // n_gpus, HKV // n_gpus
+    n_prefix_pages = PREFIX // 16
+    num_pages = n_prefix_pages + BRANCHES + 8
+
+    rt = pkg.Runtime(num_layers=L, n_heads=hq, n_kv_heads=hk, max_positions=PREFIX + 64,
+                     max_tokens=TOKENS, num_pages=num_pages, device=local)
+    rt.enable_timing(4 * L * (args.steps + args.warmup) + 64)
+    # resident prefix: seeded f16 N(0,1) in a randomly permuted page table
+    perm = np.random.default_rng(1).permutation(num_pages).astype(np.uint32)
+    rt.alloc_pages(num_pages)
+    rt.free_pages(perm[n_prefix_pages:])
+    prefix = pkg.Prefix(rt, PREFIX, pages=perm[:n_prefix_pages])
+    kp, vp = rt.pool()
+    gen = torch.Generator(device=device).manual_seed(1000 + rank)
+    for l in range(L):
+        kp[l].normal_(generator=gen)
+        vp[l].normal_(generator=gen)
+    torch.cuda.synchronize()
+    prefix.set_resident(PREFIX)
+    prefix.seal()
+    bset = pkg.BranchSet(prefix, BRANCHES, SUFFIX)
+    handles = [bset.acquire() for _ in range(BRANCHES)]
+    plan = pkg.PackPlan(prefix, bset, [(h, SUFFIX) for h in handles])
+
+    # per-layer inputs: pinned host copies (e2e leg) and device copies (value leg)
+    hq_, hk_, hv_, dq_, dk_, dv_ = [], [], [], [], [], []
+    for l in range(L):
+        q, k, v = shard_inputs(torch, l, rank, n_gpus, device)
+        hq_.append(q.pin_memory()); hk_.append(k.pin_memory()); hv_.append(v.pin_memory())
+        dq_.append(hq_[-1].to(device)); dk_.append(hk_[-1].to(device)); dv_.append(hv_[-1].to(device))
+    out_local = [torch.zeros(TOKENS, hq, D, dtype=torch.bfloat16, device=device) for _ in range(2)]
+    out_full = [torch.zeros(n_gpus, TOKENS, hq, D, dtype=torch.bfloat16, device=device)
+                for _ in range(2)] if world > 1 else None
+    out_host = torch.zeros(TOKENS, hq, D, dtype=torch.bfloat16).pin_memory()
+    stream = rt.torch_stream()
+
+    def step_device():
+        works = [None, None]
+        for l in range(L):
+            b = l & 1
+            if works[b] is not None:
+                works[b].wait()          # out_local[b] is free again (stream wait)
+            plan.attention_layer(l, dq_[l], dk_[l], dv_[l], out_local[b])
+            if world > 1:
+                works[b] = dist.all_gather_into_tensor(out_full[b].view(-1),
+                                                       out_local[b].view(-1), async_op=True)
+        for w in works:
+            if w is not None:
+                w.wait()
+
+    def step_host():
+        for l in range(L):
+            plan.attention_layer_host(l, hq_[l], hk_[l], hv_[l], out_host)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+            barrier()
+            rt.phase_times()                      # rewind the per-kernel events
+            launches0 = rt.stats().kernel_launches
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            barrier()
+            ms = e0.elapsed_time(e1)
+            phases = rt.phase_times()
+            launches = rt.stats().kernel_launches - launches0
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        n = torch.tensor([float(launches)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(n, op=dist.ReduceOp.SUM)
+        return float(t.item()), phases, int(n.item())
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms, phases, launches = timed(step_device, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    ms_e2e, _, _ = timed(step_host, max(1, min(args.steps, 3)), 1)
+    e2e_steps = max(1, min(args.steps, 3))
+    rt.synchronize()
+    status = rt.stats().device_status
+
+    result = None
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = ms / args.steps
+        value = TOKENS / (ms_per_step * 1e-3)
+        attn_ms, attn_n = phases["attention"]
+        per_launch_ms = attn_ms / max(attn_n, 1)
+        flops_per_launch = FLOPS_PER_LAYER / n_gpus
+        achieved = flops_per_launch / (per_launch_ms * 1e-3) / 1e12
+        peak = peaks["tflops_sustained"]
+        e2e_ms_per_step = ms_e2e / e2e_steps
+        qkv_bytes = L * TOKENS * (H + 2 * HKV) * D * 2
+        out_bytes = L * TOKENS * H * D * 2
+        result = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 operands, fp32 accumulate (bf16 in/out, f16 KV)",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": L, "prefix_tokens": PREFIX,
+                       "branches": BRANCHES, "suffix_tokens_per_branch": SUFFIX,
+                       "heads": "%d/%d x %d" % (H, HKV, D), "kv": "paged f16, page 16, permuted table",
+                       "sharding": "kv_heads/%d + all-gather per layer" % n_gpus,
+                       "l2": "inputs larger than L2 (8.6 GB of KV per step)"},
+            "tflops": FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12,
+            "e2e": {"value": TOKENS / (e2e_ms_per_step * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": qkv_bytes, "d2h_bytes_per_step": out_bytes,
+                    "ms_per_step": e2e_ms_per_step},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"kernel": "attention_tc_kernel", "bound": "tensor",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "peak_source": "%s bf16 sustained" % peaks["source"],
+                         "ms_per_launch": per_launch_ms, "launches": attn_n,
+                         "flops_per_launch": flops_per_launch},
+            "kernel_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
+            "device_status": status,
+        }
+    for o in (plan, bset, prefix):
+        o.close()
+    rt.close()
+    del kp, vp
+    torch.cuda.empty_cache()
+    if rank == 0:
+        if n_gpus == 1 and not args.no_extra:
+            result["extra"] = run_extras(pkg, torch, device)
+        if n_gpus == 1 and not args.no_cpu:
+            result["cpu_baseline"] = cpu_baseline(target_s=args.cpu_seconds)
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _time_calls(torch, rt, fn, reps, warmup=3):
+    stream = rt.torch_stream()
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        rt.phase_times()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps, rt.phase_times()
+
+
+def run_extras(pkg, torch, device):
+    """The other single-GPU configurations of the benchmark definition, one
+    layer each: causal prefill (TFLOP/s), 8192-prefix cascade (tokens/s),
+    paged decode (GB/s). Device-timed, inputs resident."""
+    peaks = measured_peaks()
+    extra = {}
+    g = torch.Generator(device=device).manual_seed(0)
+
+    def rnd(*shape):
+        return torch.randn(*shape, generator=g, device=device).to(torch.bfloat16)
+
+    # --- causal GQA prefill, 4096 tokens
+    T = 4096
+    rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=T,
+                     max_tokens=T, num_pages=T // 16 + 4)
+    rt.enable_timing(256)
+    prefix = pkg.Prefix(rt, T)
+    q, k, v = rnd(T, H, D), rnd(T, HKV, D), rnd(T, HKV, D)
+    out = torch.zeros(T, H, D, dtype=torch.bfloat16, device=device)
+    ms, ph = _time_calls(torch, rt, lambda: prefix.prefill_layer(0, q, k, v, out), 20)
+    flops = 4 * D * H * (T * (T + 1) // 2)
+    k_ms = ph["attention"][0] / max(ph["attention"][1], 1)
+    extra["prefill_4096"] = {
+        "ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": T / ms * 1e3,
+        "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
+        "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
+        "kvwrite_ms": ph["kvwrite"][0] / max(ph["kvwrite"][1], 1),
+        "kvwrite_gbs": T * (H + 2 * HKV) * D * 2 * 2 / 1e6 /
+                       (ph["kvwrite"][0] / max(ph["kvwrite"][1], 1))}
+    prefix.close()
+    rt.close()
+
+    # --- cascade: 8192-token resident prefix + 64 branches x 24
+    P, B, n = 8192, 64, 24
+    S = B * n
+    rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=P + 64,
+                     max_tokens=S, num_pages=P // 16 + 2 * B + 4)
+    rt.enable_timing(256)
+    prefix = pkg.Prefix(rt, P)
+    kp, vp = rt.pool()
+    kp.normal_(generator=g)
+    vp.normal_(generator=g)
+    prefix.set_resident(P)
+    prefix.seal()
+    bset = pkg.BranchSet(prefix, B, n)
+    plan = pkg.PackPlan(prefix, bset, [(bset.acquire(), n) for _ in range(B)])
+    q, k, v = rnd(S, H, D), rnd(S, HKV, D), rnd(S, HKV, D)
+    out = torch.zeros(S, H, D, dtype=torch.bfloat16, device=device)
+    ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, k, v, out), 20)
+    flops = 4 * D * H * (S * P + B * n * (n + 1) // 2)
+    k_ms = ph["attention"][0] / max(ph["attention"][1], 1)
+    extra["cascade_p8192_b64x24"] = {
+        "ms": ms, "suffix_tokens_per_s": S / ms * 1e3, "tflops": flops / ms / 1e9,
+        "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
+        "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
+        "merge_ms": ph["merge"][0] / max(ph["merge"][1], 1)}
+    for o in (plan, bset, prefix):
+        o.close()
+    rt.close()
+    del kp, vp
+
+    # --- paged decode: 256 sequences, ctx uniform in [1024, 16384] (seed 1)
+    ctx = np.random.default_rng(1).integers(1024, 16385, 256).astype(np.uint32)
+    n_pages = (ctx + 15) // 16
+    total = int(n_pages.sum())
+    rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=16400,
+                     max_tokens=256, num_pages=total + 4)
+    rt.enable_timing(256)
+    kp, vp = rt.pool()
+    kp.normal_(generator=g)
+    vp.normal_(generator=g)
+    perm = np.random.default_rng(2).permutation(total).astype(np.uint32)
+    indptr = np.concatenate([[0], np.cumsum(n_pages)]).astype(np.uint32)
+    plan = pkg.DecodePlan(rt, ctx, indptr, perm)
+    q = rnd(256, H, D)
+    out = torch.zeros(256, H, D, dtype=torch.bfloat16, device=device)
+    ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, None, None, out), 20)
+    kv_bytes = int(ctx.sum()) * 2 * HKV * D * 2
+    alg_bytes = kv_bytes + 2 * 256 * H * D * 2 + 4 * (total + 257)
+    extra["decode_256seq"] = {
+        "ms": ms, "sum_ctx": int(ctx.sum()), "algorithmic_bytes": alg_bytes,
+        "gbs": alg_bytes / ms / 1e6, "frac_of_hbm_peak": alg_bytes / ms / 1e6 / peaks["hbm_gbs"],
+        "seq_tokens_per_s": 256 / ms * 1e3,
+        "decode_kernels_ms": ph["decode"][0] / 20.0}
+    plan.close()
+    rt.close()
+    return extra
+
+
+def cpu_sample(n_branches, threads=None):
+    """One layer of the workload restricted to `n_branches` branches (16 tokens
+    each, full 32768-token prefix) through the CPU oracle. Returns seconds."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import q3_oracle as oracle
+    if threads:
+        oracle.set_threads(threads)
+    rng = np.random.default_rng(0)
+    S = n_branches * SUFFIX
+    q = rng.standard_normal((S, H, D), dtype=np.float32)
+    k = rng.standard_normal((S, HKV, D), dtype=np.float32)
+    v = rng.standard_normal((S, HKV, D), dtype=np.float32)
+    pk = rng.standard_normal((1, PREFIX, HKV, D), dtype=np.float32)
+    pv = rng.standard_normal((1, PREFIX, HKV, D), dtype=np.float32)
+    tb = np.repeat(np.arange(n_branches, dtype=np.uint32), SUFFIX)
+    tl = np.tile(np.arange(SUFFIX, dtype=np.uint32), n_branches)
+    pos = (PREFIX + tl).astype(np.uint32)
+    ones = np.ones(D, np.float32)
+    ifreq = oracle.inv_freq(1e6, D)
+    t0 = time.perf_counter()
+    qn = oracle.rms_norm(q, ones, 1e-6)
+    kn = oracle.rms_norm(k, ones, 1e-6)
+    qn, kn = oracle.rope(qn, kn, 0, pos, ifreq)
+    sk = np.zeros((n_branches, 1, SUFFIX, HKV * D), np.float32)
+    sv = np.zeros_like(sk)
+    oracle.kv_scatter(sk, sv, kn, v, tb, tl, SUFFIX, 1, 0)
+    oracle.attention_segmented(qn, pk, pv, PREFIX, PREFIX, sk, sv, SUFFIX, 1, 0, tb, tl,
+                               HKV, np.float32(1 / np.sqrt(D)))
+    return time.perf_counter() - t0, oracle.threads()
+
+
+def cpu_baseline(target_s=15.0):
+    t1, threads = cpu_sample(1)
+    nb = int(max(1, min(BRANCHES, target_s / max(t1, 1e-3))))
+    t = t1 if nb == 1 else cpu_sample(nb)[0]
+    tokens = nb * SUFFIX
+    return {"value": tokens / (t * L), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": "1 of %d layers, %d of %d branches x %d tokens over the full %d-token "
+                      "prefix, fp32 contiguous KV, %.1f s; scaled by the layer count"
+                      % (L, nb, BRANCHES, SUFFIX, PREFIX, t)}
+
+
+def run_reference(args):
+    """The reference arm: the path's CPU implementation (the oracle port of the
+    reference kernels; the reference ships no CPU attention of its own) on all
+    host threads. Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    times = []
+    t1, threads = cpu_sample(1)
+    # a step = a bounded sample sized to a few seconds
+    nb = int(max(1, min(BRANCHES, 4.0 / max(t1, 1e-3))))
+    for i in range(args.warmup + args.steps):
+        t, _ = cpu_sample(nb)
+        if i >= args.warmup:
+            times.append(t)
+    t = float(np.mean(times))
+    tokens = nb * SUFFIX
+    value = tokens / (t * L)
+    sample = ("1 of %d layers, %d of %d branches x %d tokens over the full %d-token prefix "
+              "per step; scaled by the layer count" % (L, nb, BRANCHES, SUFFIX, PREFIX))
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp32 (double accumulation)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": L, "prefix_tokens": PREFIX,
+                   "branches": BRANCHES, "suffix_tokens_per_branch": SUFFIX},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the single-layer prefill / cascade / decode lines")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

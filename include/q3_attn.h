@@ -160,6 +160,19 @@ typedef struct {
 } q3_attn_stats;
 void q3_attn_get_stats(const q3_attn_runtime *rt, q3_attn_stats *stats);
 
+/* Per-kernel device times, the counterpart of the reference's phase events
+ * (ref: q3_forward_stats qk_norm_ms/rope_ms/attention_ms, src/q3_forward.h:50-75;
+ * events at src/q3_forward.cu:1205-1285). When enabled, every launch is
+ * bracketed by an event pair on the runtime's stream (up to `max_launches`
+ * pairs, created here, none in the warm path). q3_attn_phase_times
+ * synchronises the stream, SUMS the pairs recorded since the last call per
+ * phase, and rewinds. Phases: 0 fused norm+rope+KV write, 1 tensor-core
+ * attention, 2 partial merge, 3 paged decode (+ its merge). */
+bool q3_attn_enable_timing(q3_attn_runtime *rt, uint32_t max_launches, char *error,
+                           size_t error_len);
+bool q3_attn_phase_times(q3_attn_runtime *rt, double ms_out[4],
+                         uint64_t launches_out[4], char *error, size_t error_len);
+
 /* --- paged KV: page pool ------------------------------------------- *
  * Physical layout, K and V alike: [layer][kv_head][page][16 tokens][128] f16,
  * so one page of one head is 4 KiB contiguous and a KV-head shard is a

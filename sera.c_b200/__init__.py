@@ -143,6 +143,18 @@ class Runtime:
         lib().q3_attn_get_stats(self.h, ctypes.byref(s))
         return s
 
+    PHASES = ("kvwrite", "attention", "merge", "decode")
+
+    def enable_timing(self, max_launches=4096):
+        _call(lib().q3_attn_enable_timing, self.h, max_launches)
+
+    def phase_times(self):
+        """{phase: (summed ms, launches)} since the last call; synchronises."""
+        ms = (ctypes.c_double * 4)()
+        n = (ctypes.c_uint64 * 4)()
+        _call(lib().q3_attn_phase_times, self.h, ms, n)
+        return {name: (ms[i], int(n[i])) for i, name in enumerate(self.PHASES)}
+
     def alloc_pages(self, n):
         out = np.empty(n, np.uint32)
         _call(lib().q3_pages_alloc, self.h, n, out.ctypes.data_as(_c_u32p))

@@ -60,6 +60,9 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     sig("q3_attn_stream", vp, [vp])
     sig("q3_attn_synchronize", b, [vp] + err)
     sig("q3_attn_get_stats", None, [vp, ctypes.POINTER(AttnStats)])
+    sig("q3_attn_enable_timing", b, [vp, u32] + err)
+    sig("q3_attn_phase_times", b, [vp, ctypes.POINTER(ctypes.c_double),
+                                   ctypes.POINTER(ctypes.c_uint64)] + err)
     sig("q3_pages_alloc", b, [vp, u32, up] + err)
     sig("q3_pages_free", None, [vp, up, u32])
     sig("q3_pages_k", vp, [vp])

@@ -378,15 +378,19 @@ bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer, const q3_decode_plan 
     p.part_ml = rt->dec_ml;
     p.status = rt->status_dev;
     dim3 grid(plan->n_work, c.n_kv_heads);
+    q3_phase_begin(rt, Q3_PHASE_DECODE);
     decode_attention_kernel<<<grid, kDecThreads, kDecSmemTotal, rt->stream>>>(
         rt->k_map, rt->v_map, p);
+    q3_phase_end(rt);
     Q3_LAUNCH_CHECK("decode_attention launch failed");
     rt->n_launch++;
     if (plan->n_work > plan->num_seqs) {
         const uint32_t warps = plan->num_seqs * c.n_heads;
+        q3_phase_begin(rt, Q3_PHASE_DECODE);
         decode_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, rt->stream>>>(
             plan->seq_work_begin, plan->num_seqs, c.n_heads, c.n_kv_heads, rt->dec_o,
             rt->dec_ml, c.out_fp32, out_bf16);
+        q3_phase_end(rt);
         Q3_LAUNCH_CHECK("decode_merge launch failed");
         rt->n_launch++;
     }

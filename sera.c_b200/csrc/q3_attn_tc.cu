@@ -606,15 +606,19 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st
     p.part_o = rt->part_o;
     p.part_ml = rt->part_ml;
     p.status = rt->status_dev;
+    q3_phase_begin(rt, Q3_PHASE_ATTENTION);
     attention_tc_kernel<<<st->grid, kThreads, kSmemTotal, rt->stream>>>(q_map, rt->k_map,
                                                                        rt->v_map, p);
+    q3_phase_end(rt);
     Q3_LAUNCH_CHECK("attention_tc launch failed");
     rt->n_launch++;
     if (st->n_merges) {
         dim3 grid(st->n_merges, 8);
+        q3_phase_begin(rt, Q3_PHASE_MERGE);
         merge_partials_kernel<<<grid, 256, 0, rt->stream>>>(
             st->merges, rt->part_o, rt->part_ml, st->tokens, c.n_heads, c.out_fp32,
             out_bf16);
+        q3_phase_end(rt);
         Q3_LAUNCH_CHECK("merge_partials launch failed");
         rt->n_launch++;
     }

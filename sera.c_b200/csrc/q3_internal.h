@@ -90,7 +90,31 @@ struct q3_attn_runtime {
 
     uint64_t n_alloc, n_free, n_sync, n_launch;
     uint64_t workspace_bytes;
+
+    /* optional per-kernel timing: event pairs recorded around launches, read
+     * after a synchronize (the reference brackets its phases the same way,
+     * ref: src/q3_forward.cu:1205-1285,1759-1822) */
+    bool timing_on;
+    std::vector<cudaEvent_t> ev;      /* pairs: [2i] start, [2i+1] stop */
+    std::vector<uint8_t> ev_phase;    /* phase of pair i */
+    size_t ev_used;                   /* pairs recorded */
 };
+
+enum { Q3_PHASE_KVWRITE = 0, Q3_PHASE_ATTENTION = 1, Q3_PHASE_MERGE = 2,
+       Q3_PHASE_DECODE = 3, Q3_PHASE_COUNT = 4 };
+
+static inline void q3_phase_begin(q3_attn_runtime *rt, int phase) {
+    if (rt->timing_on && rt->ev_used < rt->ev_phase.size()) {
+        rt->ev_phase[rt->ev_used] = (uint8_t)phase;
+        cudaEventRecord(rt->ev[2 * rt->ev_used], rt->stream);
+    }
+}
+static inline void q3_phase_end(q3_attn_runtime *rt) {
+    if (rt->timing_on && rt->ev_used < rt->ev_phase.size()) {
+        cudaEventRecord(rt->ev[2 * rt->ev_used + 1], rt->stream);
+        rt->ev_used++;
+    }
+}
 
 struct q3_prefix_kv {
     q3_attn_runtime *rt;

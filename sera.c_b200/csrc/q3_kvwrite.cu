@@ -120,11 +120,13 @@ bool q3_launch_kvwrite(q3_attn_runtime *rt, uint32_t layer, const void *q,
     if (threads == 0) return true;
     const size_t layer_off = (size_t)layer * c.n_kv_heads * c.num_pages * Q3_PAGE * Q3_D;
     const unsigned grid = (unsigned)((threads + 255) / 256);
+    q3_phase_begin(rt, Q3_PHASE_KVWRITE);
     qknorm_rope_kvwrite_kernel<<<grid, 256, 0, rt->stream>>>(
         (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v,
         tokens, c.n_heads, c.n_kv_heads, rt->qk_norm_w + (size_t)layer * 2 * Q3_D,
         c.rms_eps, rt->rope_table, rope_pos, dst_page, dst_slot, (__half *)q_out,
         rt->k_pool + layer_off, rt->v_pool + layer_off, c.num_pages, q_rows, kv_rows);
+    q3_phase_end(rt);
     Q3_LAUNCH_CHECK("qknorm_rope_kvwrite launch failed");
     rt->n_launch++;
     return true;

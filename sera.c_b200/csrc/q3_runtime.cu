@@ -167,6 +167,8 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     rt->host_stage_bytes = rt->dev_stage_bytes = 0;
     rt->n_alloc = rt->n_free = rt->n_sync = rt->n_launch = 0;
     rt->workspace_bytes = 0;
+    rt->timing_on = false;
+    rt->ev_used = 0;
 
     const size_t pool_bytes = (size_t)pool_rows * Q3_D * sizeof(__half);
     const size_t q2_bytes = (size_t)c.max_tokens * c.n_heads * Q3_D * sizeof(__half);
@@ -258,6 +260,7 @@ extern "C" void q3_attn_destroy(q3_attn_runtime *rt) {
     rt_free(rt, rt->rope_table);
     rt_free(rt, rt->status_dev);
     rt_free(rt, rt->dev_stage);
+    for (cudaEvent_t e : rt->ev) cudaEventDestroy(e);
     if (rt->host_stage) cudaFreeHost(rt->host_stage);
     if (rt->status_host) cudaFreeHost(rt->status_host);
     if (rt->stream) cudaStreamDestroy(rt->stream);
@@ -304,6 +307,47 @@ extern "C" bool q3_attn_synchronize(q3_attn_runtime *rt, char *error,
                      *rt->status_host);
         return false;
     }
+    return true;
+}
+
+extern "C" bool q3_attn_enable_timing(q3_attn_runtime *rt, uint32_t max_launches,
+                                      char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt || max_launches == 0)
+        return q3_fail(error, error_len, "q3_attn_enable_timing: invalid argument");
+    while (rt->ev.size() < 2 * (size_t)max_launches) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess)
+            return q3_fail(error, error_len, "q3_attn_enable_timing: cudaEventCreate failed");
+        rt->ev.push_back(e);
+    }
+    rt->ev_phase.assign(rt->ev.size() / 2, 0);
+    rt->ev_used = 0;
+    rt->timing_on = true;
+    return true;
+}
+
+extern "C" bool q3_attn_phase_times(q3_attn_runtime *rt, double ms_out[4],
+                                    uint64_t launches_out[4], char *error,
+                                    size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt || !ms_out || !launches_out)
+        return q3_fail(error, error_len, "q3_attn_phase_times: invalid argument");
+    for (int i = 0; i < Q3_PHASE_COUNT; i++) {
+        ms_out[i] = 0.0;
+        launches_out[i] = 0;
+    }
+    cudaError_t e = cudaStreamSynchronize(rt->stream);
+    rt->n_sync++;
+    if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "q3_attn_phase_times", e);
+    for (size_t i = 0; i < rt->ev_used; i++) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, rt->ev[2 * i], rt->ev[2 * i + 1]) != cudaSuccess)
+            return q3_fail(error, error_len, "q3_attn_phase_times: cudaEventElapsedTime failed");
+        ms_out[rt->ev_phase[i]] += ms;
+        launches_out[rt->ev_phase[i]]++;
+    }
+    rt->ev_used = 0;
     return true;
 }
 

@@ -108,7 +108,12 @@ def run_case_native(pkg, case, out_fp32=False, prefill_chunks=None, permute_page
 # ---------------------------------------------------------------------------
 
 def ref_lib():
-    path = os.path.join(ROOT, "oracle", "_ref", "libq3ref.so")
+    return fp32_surface(os.path.join(ROOT, "oracle", "_ref", "libq3ref.so"))
+
+
+def fp32_surface(path):
+    """ctypes view of the fp32 primitive symbols, which the reference's library
+    and this repository's library both export under the same names."""
     if not os.path.exists(path):
         return None
     L = ctypes.CDLL(path)

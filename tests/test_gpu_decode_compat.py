@@ -125,7 +125,7 @@ def test_fp32_surface_matches_oracle_and_reference(pkg, name):
     case = _cases.make_case(name)
     ifreq = oracle.inv_freq(case.theta, case.D)
     ref = oracle.run_case(case)
-    mine = harness.run_case_fp32_surface(ctypes.CDLL(pkg.lib_path()), case, ifreq)
+    mine = harness.run_case_fp32_surface(harness.fp32_surface(pkg.lib_path()), case, ifreq)
     # the reference's own tolerance for its primitives is 1e-4
     assert np.abs(mine["q2"] - ref["q2"]).max() < 1e-4
     assert np.abs(mine["k2"] - ref["k2"]).max() < 1e-4
@@ -134,11 +134,15 @@ def test_fp32_surface_matches_oracle_and_reference(pkg, name):
     if L is None:
         pytest.skip("oracle/_ref/libq3ref.so not built (reference checkout absent)")
     theirs = harness.run_case_fp32_surface(L, case, ifreq)
-    # the reference's kernels against the oracle: this pins the oracle
-    assert np.abs(theirs["q2"] - ref["q2"]).max() < 1e-4
-    assert np.abs(theirs["k2"] - ref["k2"]).max() < 1e-4
-    assert np.abs(theirs["out"] - ref["out"]).max() < 1e-4
-    assert np.abs(theirs["out"] - mine["out"]).max() < 1e-4
+    # The reference's kernels against the oracle: this pins the oracle. The
+    # reference is built with --use_fast_math (its Makefile), so its rope uses
+    # the __sinf/__cosf intrinsics, whose absolute error grows with the angle
+    # (its own test stops at position 14; these cases reach position 263):
+    # 5e-4 instead of its 1e-4.
+    assert np.abs(theirs["q2"] - ref["q2"]).max() < 5e-4
+    assert np.abs(theirs["k2"] - ref["k2"]).max() < 5e-4
+    assert np.abs(theirs["out"] - ref["out"]).max() < 5e-4
+    assert np.abs(theirs["out"] - mine["out"]).max() < 5e-4
 
 
 def test_fp32_kv_cache_split_equals_contiguous(pkg):
