@@ -313,44 +313,44 @@ def _time_calls(torch, rt, fn, reps, warmup=3):
         return e0.elapsed_time(e1) / reps, rt.phase_times()
 
 
-def run_extras(pkg, torch, device):
-    """The other single-GPU configurations of the benchmark definition, one
-    layer each: causal prefill (TFLOP/s), 8192-prefix cascade (tokens/s),
-    paged decode (GB/s). Device-timed, inputs resident."""
+def case_prefill(pkg, torch, device, T=4096, reps=20):
+    """Causal GQA prefill of T tokens, one layer (fused norm+rope+KV write, then
+    attention over the pages just written)."""
     peaks = measured_peaks()
-    extra = {}
     g = torch.Generator(device=device).manual_seed(0)
-
-    def rnd(*shape):
-        return torch.randn(*shape, generator=g, device=device).to(torch.bfloat16)
-
-    # --- causal GQA prefill, 4096 tokens
-    T = 4096
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=device).to(torch.bfloat16)
     rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=T,
-                     max_tokens=T, num_pages=T // 16 + 4)
-    rt.enable_timing(256)
+                     max_tokens=T, num_pages=T // 16 + 4, device=device.index)
+    rt.enable_timing(16 * reps + 64)
     prefix = pkg.Prefix(rt, T)
     q, k, v = rnd(T, H, D), rnd(T, HKV, D), rnd(T, HKV, D)
     out = torch.zeros(T, H, D, dtype=torch.bfloat16, device=device)
-    ms, ph = _time_calls(torch, rt, lambda: prefix.prefill_layer(0, q, k, v, out), 20)
+    ms, ph = _time_calls(torch, rt, lambda: prefix.prefill_layer(0, q, k, v, out), reps)
     flops = 4 * D * H * (T * (T + 1) // 2)
     k_ms = ph["attention"][0] / max(ph["attention"][1], 1)
-    extra["prefill_4096"] = {
-        "ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": T / ms * 1e3,
-        "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
-        "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
-        "kvwrite_ms": ph["kvwrite"][0] / max(ph["kvwrite"][1], 1),
-        "kvwrite_gbs": T * (H + 2 * HKV) * D * 2 * 2 / 1e6 /
-                       (ph["kvwrite"][0] / max(ph["kvwrite"][1], 1))}
+    w_ms = ph["kvwrite"][0] / max(ph["kvwrite"][1], 1)
+    res = {"tokens": T, "ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": T / ms * 1e3,
+           "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
+           "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
+           "merge_ms": ph["merge"][0] / max(ph["merge"][1], 1),
+           "kvwrite_ms": w_ms, "kvwrite_algorithmic_bytes": T * (H + 2 * HKV) * D * 2 * 2,
+           "kvwrite_gbs": T * (H + 2 * HKV) * D * 2 * 2 / 1e6 / w_ms,
+           "kvwrite_frac_of_hbm_peak": T * (H + 2 * HKV) * D * 2 * 2 / 1e6 / w_ms / peaks["hbm_gbs"]}
     prefix.close()
     rt.close()
+    return res
 
-    # --- cascade: 8192-token resident prefix + 64 branches x 24
-    P, B, n = 8192, 64, 24
+
+def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20):
+    """Shared-prefix + packed-suffix attention, one layer, prefix resident."""
+    peaks = measured_peaks()
+    g = torch.Generator(device=device).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=device).to(torch.bfloat16)
     S = B * n
-    rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=P + 64,
-                     max_tokens=S, num_pages=P // 16 + 2 * B + 4)
-    rt.enable_timing(256)
+    ppb = (n + 15) // 16
+    rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=P + n + 8,
+                     max_tokens=S, num_pages=P // 16 + ppb * B + 4, device=device.index)
+    rt.enable_timing(16 * reps + 64)
     prefix = pkg.Prefix(rt, P)
     kp, vp = rt.pool()
     kp.normal_(generator=g)
@@ -361,45 +361,79 @@ def run_extras(pkg, torch, device):
     plan = pkg.PackPlan(prefix, bset, [(bset.acquire(), n) for _ in range(B)])
     q, k, v = rnd(S, H, D), rnd(S, HKV, D), rnd(S, HKV, D)
     out = torch.zeros(S, H, D, dtype=torch.bfloat16, device=device)
-    ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, k, v, out), 20)
+    ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, k, v, out), reps)
     flops = 4 * D * H * (S * P + B * n * (n + 1) // 2)
     k_ms = ph["attention"][0] / max(ph["attention"][1], 1)
-    extra["cascade_p8192_b64x24"] = {
-        "ms": ms, "suffix_tokens_per_s": S / ms * 1e3, "tflops": flops / ms / 1e9,
-        "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
-        "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
-        "merge_ms": ph["merge"][0] / max(ph["merge"][1], 1)}
+    res = {"prefix": P, "branches": B, "suffix": n, "ms": ms,
+           "suffix_tokens_per_s": S / ms * 1e3, "tflops": flops / ms / 1e9,
+           "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
+           "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
+           "merge_ms": ph["merge"][0] / max(ph["merge"][1], 1),
+           "kvwrite_ms": ph["kvwrite"][0] / max(ph["kvwrite"][1], 1)}
     for o in (plan, bset, prefix):
         o.close()
     rt.close()
-    del kp, vp
+    return res
 
-    # --- paged decode: 256 sequences, ctx uniform in [1024, 16384] (seed 1)
-    ctx = np.random.default_rng(1).integers(1024, 16385, 256).astype(np.uint32)
+
+def case_decode(pkg, torch, device, n_seqs=256, reps=20):
+    """Paged decode: n_seqs sequences, ctx uniform in [1024, 16384]
+    (numpy default_rng(1)), randomly permuted pages, one query token each."""
+    peaks = measured_peaks()
+    g = torch.Generator(device=device).manual_seed(0)
+    ctx = np.random.default_rng(1).integers(1024, 16385, 256).astype(np.uint32)[:n_seqs]
     n_pages = (ctx + 15) // 16
     total = int(n_pages.sum())
     rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=16400,
-                     max_tokens=256, num_pages=total + 4)
-    rt.enable_timing(256)
+                     max_tokens=n_seqs, num_pages=total + 4, device=device.index)
+    rt.enable_timing(16 * reps + 64)
     kp, vp = rt.pool()
     kp.normal_(generator=g)
     vp.normal_(generator=g)
     perm = np.random.default_rng(2).permutation(total).astype(np.uint32)
     indptr = np.concatenate([[0], np.cumsum(n_pages)]).astype(np.uint32)
     plan = pkg.DecodePlan(rt, ctx, indptr, perm)
-    q = rnd(256, H, D)
-    out = torch.zeros(256, H, D, dtype=torch.bfloat16, device=device)
-    ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, None, None, out), 20)
+    q = torch.randn(n_seqs, H, D, generator=g, device=device).to(torch.bfloat16)
+    out = torch.zeros(n_seqs, H, D, dtype=torch.bfloat16, device=device)
+    ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, None, None, out), reps)
     kv_bytes = int(ctx.sum()) * 2 * HKV * D * 2
-    alg_bytes = kv_bytes + 2 * 256 * H * D * 2 + 4 * (total + 257)
-    extra["decode_256seq"] = {
-        "ms": ms, "sum_ctx": int(ctx.sum()), "algorithmic_bytes": alg_bytes,
-        "gbs": alg_bytes / ms / 1e6, "frac_of_hbm_peak": alg_bytes / ms / 1e6 / peaks["hbm_gbs"],
-        "seq_tokens_per_s": 256 / ms * 1e3,
-        "decode_kernels_ms": ph["decode"][0] / 20.0}
+    alg_bytes = kv_bytes + 2 * n_seqs * H * D * 2 + 4 * (total + n_seqs + 1)
+    res = {"sequences": n_seqs, "ms": ms, "sum_ctx": int(ctx.sum()),
+           "algorithmic_bytes": alg_bytes, "gbs": alg_bytes / ms / 1e6,
+           "frac_of_hbm_peak": alg_bytes / ms / 1e6 / peaks["hbm_gbs"],
+           "seq_tokens_per_s": n_seqs / ms * 1e3,
+           "decode_kernels_ms": ph["decode"][0] / reps}
     plan.close()
     rt.close()
-    return extra
+    return res
+
+
+CASES = {
+    "prefill_4096": lambda pkg, torch, dev, reps: case_prefill(pkg, torch, dev, 4096, reps),
+    "cascade_p8192_b64x24": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, 8192, 64, 24, reps),
+    "stack_layer_p32768_b128x16": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, PREFIX, BRANCHES, SUFFIX, reps),
+    "decode_256seq": lambda pkg, torch, dev, reps: case_decode(pkg, torch, dev, 256, reps),
+    "decode_64seq": lambda pkg, torch, dev, reps: case_decode(pkg, torch, dev, 64, reps),
+}
+
+
+def run_extras(pkg, torch, device):
+    """The other single-GPU configurations of the benchmark definition, one
+    layer each: causal prefill (TFLOP/s), 8192-prefix cascade (tokens/s),
+    paged decode (GB/s). Device-timed, inputs resident."""
+    return {name: CASES[name](pkg, torch, device, 20)
+            for name in ("prefill_4096", "cascade_p8192_b64x24", "decode_256seq")}
+
+
+def run_case(args):
+    """One small single-layer case on its own (used for profiler captures)."""
+    import torch
+    import __graft_entry__ as entry
+    entry.build()
+    pkg = entry.load_package()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    print(json.dumps({"case": args.case, **CASES[args.case](pkg, torch, device, args.reps)}))
 
 
 def cpu_sample(n_branches, threads=None):
@@ -487,8 +521,13 @@ def main():
                     help="skip the single-layer prefill / cascade / decode lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--case", choices=sorted(CASES), default=None,
+                    help="run only this single-layer case (for profiler captures)")
+    ap.add_argument("--reps", type=int, default=5)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
