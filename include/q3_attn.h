@@ -302,6 +302,47 @@ bool q3_decode_attention_layer(q3_decode_plan *plan, uint32_t layer,
                                const void *v_new, void *out, char *error,
                                size_t error_len);
 
+/* --- decode without any allocation ------------------------------------ *
+ * No counterpart in the reference. For callers that cannot allocate device
+ * memory when they need attention (a server that gave the whole heap to its own
+ * arena, a process under a no-cudaMalloc-after-start-up rule, a plugin that
+ * must not re-enter the host's allocator): the split-KV partials of the decode
+ * kernel live in a fixed array inside the library (about 8.5 MB per GPU, held
+ * until the process exits) instead of a runtime-owned buffer. The call
+ * allocates nothing, on host or device, and needs no q3_attn_runtime: every
+ * buffer is the caller's.
+ *   q_f16        [num_seqs][n_heads][128] f16, already normalised and roped
+ *                (e.g. by q3_cuda_qknorm_rope_kvwrite)
+ *   k_pages/v_pages  one layer of a page pool, [n_kv_heads][num_pages][16][128] f16
+ *   ctx_lens, page_indptr, page_indices, work, seq_work_begin: DEVICE arrays;
+ *                work / seq_work_begin are produced on the host by
+ *                q3_decode_work_host and copied by the caller
+ *   out_bf16     [num_seqs][n_heads][128] bf16
+ * Limit: n_work * n_kv_heads <= Q3_DECODE_NOALLOC_MAX_SLOTS, else the call
+ * fails with a message. The first call on each device looks up the array's
+ * device address; make that call before any stream capture. All calls share the
+ * array: two calls that overlap on the GPU race. Nothing in it needs clearing
+ * (every slot a call reads was written by that call). */
+#define Q3_DECODE_NOALLOC_MAX_SLOTS 2048u
+typedef struct {
+    uint32_t seq;
+    uint32_t page_begin;
+    uint32_t page_end;
+    uint32_t slot;
+} q3_decode_work_item;
+/* Pure host: cut sequences into chunks of at most 64 pages. work_out holds up
+ * to max_work items, seq_work_begin_out num_seqs + 1 entries. Returns the
+ * number of work items, or -1. */
+int64_t q3_decode_work_host(const uint32_t *ctx_lens, uint32_t num_seqs,
+                            q3_decode_work_item *work_out, uint32_t max_work,
+                            uint32_t *seq_work_begin_out, char *error, size_t error_len);
+bool q3_cuda_attention_decode_noalloc(
+    const void *q_f16, const void *k_pages, const void *v_pages, uint32_t num_pages,
+    const uint32_t *ctx_lens, const uint32_t *page_indptr, const uint32_t *page_indices,
+    const q3_decode_work_item *work, uint32_t n_work, const uint32_t *seq_work_begin,
+    uint32_t num_seqs, uint32_t n_heads, uint32_t n_kv_heads, void *out_bf16,
+    void *stream, char *error, size_t error_len);
+
 /* --- low-level fused KV write (new kernel; replaces ref a1+a2/a3+a5/a8:
  *     two rms_norm launches, rope, and the append / scatter) -------------- *
  * Per token t: rope position rope_pos[t], destination page dst_page[t] and

@@ -313,6 +313,28 @@ class DecodePlan:
               _ptr(v_new), _ptr(out))
 
 
+def decode_work_host(ctx_lens):
+    """q3_decode_work_host: (work [n,4] uint32, seq_work_begin [S+1] uint32)."""
+    a, pa = _u32(ctx_lens)
+    cap = int(sum((int(c) + 15) // 16 // 64 + 2 for c in a))
+    work = np.zeros((cap, 4), np.uint32)
+    swb = np.zeros(len(a) + 1, np.uint32)
+    n = _call(lib().q3_decode_work_host, pa, len(a), work.ctypes.data_as(ctypes.c_void_p),
+              cap, swb.ctypes.data_as(_c_u32p))
+    return work[:n].copy(), swb
+
+
+def attention_decode_noalloc(q_f16, k_pages, v_pages, ctx_lens, page_indptr, page_indices,
+                             work, seq_work_begin, out_bf16, stream_ptr=None):
+    """q3_cuda_attention_decode_noalloc: every argument is a CUDA tensor owned by
+    the caller; the call allocates nothing."""
+    n_kv_heads, num_pages = k_pages.shape[0], k_pages.shape[1]
+    _call(lib().q3_cuda_attention_decode_noalloc, _ptr(q_f16), _ptr(k_pages), _ptr(v_pages),
+          num_pages, _ptr(ctx_lens), _ptr(page_indptr), _ptr(page_indices), _ptr(work),
+          work.shape[0], _ptr(seq_work_begin), q_f16.shape[0], q_f16.shape[1], n_kv_heads,
+          _ptr(out_bf16), ctypes.c_void_p(stream_ptr) if stream_ptr else None)
+
+
 def pack_suffix_host(items, prefix_len, max_branches, max_suffix):
     """q3_pack_suffix_host: the reference's q3_decide_run packing, pure host."""
     arr = (SuffixItem * len(items))(*[SuffixItem(b, n) for b, n in items])

@@ -103,6 +103,9 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     sig("q3_decode_plan_create", vp, [vp, up, up, up, u32] + err)
     sig("q3_decode_plan_destroy", None, [vp])
     sig("q3_decode_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_decode_work_host", ctypes.c_int64, [up, u32, vp, u32, up] + err)
+    sig("q3_cuda_attention_decode_noalloc", b,
+        [vp, vp, vp, u32, vp, vp, vp, vp, u32, vp, u32, u32, u32, vp, vp] + err)
     sig("q3_cuda_qknorm_rope_kvwrite", b, [vp, u32, vp, vp, vp, u32, vp, vp, vp, vp] + err)
     sig("q3_schedule_describe", b,
         [u32, u32, u32, up, up, u32, u32, u32, u32, ctypes.POINTER(SchedSummary),

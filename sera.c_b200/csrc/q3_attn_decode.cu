@@ -396,3 +396,135 @@ bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer, const q3_decode_plan 
     }
     return true;
 }
+
+/* ------------------------------------------------------------------------
+ * Allocation-free decode entry point.
+ *
+ * Some hosts may not allocate device memory at the time they need attention:
+ * a serving loop that has handed the whole device heap to its own arena, code
+ * running under a memory budget that forbids cudaMalloc after start-up, or a
+ * plugin loaded into a process whose allocator must not be re-entered. For
+ * them the split-KV partials live in the fixed arrays below instead of a
+ * buffer the runtime would allocate. Every GPU that loads this library holds
+ * these arrays (about 8.5 MB) until the process exits.
+ * ------------------------------------------------------------------------ */
+#define Q3_NOALLOC_SLOTS Q3_DECODE_NOALLOC_MAX_SLOTS
+
+static __device__ __align__(256) float q3_noalloc_part_o[(size_t)Q3_NOALLOC_SLOTS * Q3_G * Q3_D];
+static __device__ __align__(256) float2 q3_noalloc_part_ml[(size_t)Q3_NOALLOC_SLOTS * Q3_G];
+static __device__ __align__(256) uint32_t q3_noalloc_status[64];
+
+namespace {
+struct NoallocDevice {
+    bool ready;
+    float *part_o;
+    float2 *part_ml;
+    uint32_t *status;
+};
+NoallocDevice g_noalloc[64];
+}  // namespace
+
+static_assert(sizeof(q3_decode_work_item) == sizeof(q3_decode_work),
+              "public and internal work items must have one layout");
+
+extern "C" int64_t q3_decode_work_host(const uint32_t *ctx_lens, uint32_t num_seqs,
+                                       q3_decode_work_item *work_out, uint32_t max_work,
+                                       uint32_t *seq_work_begin_out, char *error,
+                                       size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!ctx_lens || !work_out || !seq_work_begin_out || num_seqs == 0) {
+        q3_fail(error, error_len, "q3_decode_work_host: invalid argument");
+        return -1;
+    }
+    std::vector<q3_decode_work> work;
+    std::vector<uint32_t> swb;
+    q3_build_decode_work(ctx_lens, num_seqs, 0, 64, work, swb);
+    if (work.size() > max_work) {
+        q3_fail(error, error_len, "q3_decode_work_host: work list does not fit");
+        return -1;
+    }
+    memcpy(work_out, work.data(), work.size() * sizeof(q3_decode_work));
+    memcpy(seq_work_begin_out, swb.data(), swb.size() * sizeof(uint32_t));
+    return (int64_t)work.size();
+}
+
+extern "C" bool q3_cuda_attention_decode_noalloc(
+    const void *q_f16, const void *k_pages, const void *v_pages, uint32_t num_pages,
+    const uint32_t *ctx_lens, const uint32_t *page_indptr, const uint32_t *page_indices,
+    const q3_decode_work_item *work, uint32_t n_work, const uint32_t *seq_work_begin,
+    uint32_t num_seqs, uint32_t n_heads, uint32_t n_kv_heads, void *out_bf16,
+    void *stream, char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!q_f16 || !k_pages || !v_pages || !ctx_lens || !page_indptr || !page_indices ||
+        !work || !seq_work_begin || !out_bf16 || num_seqs == 0 || n_work < num_seqs ||
+        num_pages == 0 || n_kv_heads == 0 || n_heads != n_kv_heads * Q3_G)
+        return q3_fail(error, error_len, "q3_cuda_attention_decode_noalloc: invalid argument");
+    if ((uint64_t)n_work * n_kv_heads > Q3_NOALLOC_SLOTS) {
+        if (error && error_len)
+            snprintf(error, error_len,
+                     "q3_cuda_attention_decode_noalloc: %u work items x %u KV heads exceed the "
+                     "fixed scratch of %u slots",
+                     n_work, n_kv_heads, (unsigned)Q3_NOALLOC_SLOTS);
+        return false;
+    }
+    const uint64_t rows = (uint64_t)n_kv_heads * num_pages * Q3_PAGE;
+    if (rows >= (1ull << 31))
+        return q3_fail(error, error_len, "q3_cuda_attention_decode_noalloc: pool too large");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return q3_fail(error, error_len, "q3_cuda_attention_decode_noalloc: no current device");
+    NoallocDevice &nd = g_noalloc[dev];
+    if (!nd.ready) {
+        /* First call on this device: the array names above are host-side
+         * stand-ins, not device addresses; ask the runtime for the addresses
+         * once, with this device current. */
+        cudaError_t e = cudaGetSymbolAddress((void **)&nd.part_o, q3_noalloc_part_o);
+        if (e == cudaSuccess)
+            e = cudaGetSymbolAddress((void **)&nd.part_ml, q3_noalloc_part_ml);
+        if (e == cudaSuccess)
+            e = cudaGetSymbolAddress((void **)&nd.status, q3_noalloc_status);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(decode_attention_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kDecSmemTotal);
+        if (e != cudaSuccess)
+            return q3_fail_cuda(error, error_len,
+                                "q3_cuda_attention_decode_noalloc: device set-up", e);
+        nd.ready = true;
+    }
+    CUtensorMap k_map, v_map;   /* host-side encoding, no device memory involved */
+    if (!q3_encode_tmap_2d(&k_map, k_pages, Q3_D, rows, 64, Q3_PAGE, error, error_len) ||
+        !q3_encode_tmap_2d(&v_map, v_pages, Q3_D, rows, 64, Q3_PAGE, error, error_len))
+        return false;
+    DecodeParams p;
+    p.work = reinterpret_cast<const q3_decode_work *>(work);
+    p.seq_work_begin = seq_work_begin;
+    p.ctx_lens = ctx_lens;
+    p.page_indptr = page_indptr;
+    p.page_indices = page_indices;
+    p.q2 = (const __half *)q_f16;
+    p.n_heads = n_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.num_pages = num_pages;
+    p.pool_row_base = 0;
+    p.pool_rows_total = (uint32_t)rows;
+    p.extra_token = 0;
+    p.scale_log2 = (1.0f / sqrtf((float)Q3_D)) * 1.4426950408889634f;
+    p.out_fp32 = 0;
+    p.out = out_bf16;
+    p.part_o = nd.part_o;
+    p.part_ml = nd.part_ml;
+    p.status = nd.status;
+    dim3 grid(n_work, n_kv_heads);
+    decode_attention_kernel<<<grid, kDecThreads, kDecSmemTotal, (cudaStream_t)stream>>>(
+        k_map, v_map, p);
+    Q3_LAUNCH_CHECK("q3_cuda_attention_decode_noalloc: launch failed");
+    if (n_work > num_seqs) {
+        const uint32_t warps = num_seqs * n_heads;
+        decode_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+            seq_work_begin, num_seqs, n_heads, n_kv_heads, nd.part_o, nd.part_ml, 0u,
+            out_bf16);
+        Q3_LAUNCH_CHECK("q3_cuda_attention_decode_noalloc: merge launch failed");
+    }
+    return true;
+}
