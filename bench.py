@@ -121,10 +121,8 @@ def shard_inputs(torch, layer, rank, n_gpus, device):
     q = torch.randn(TOKENS, H, D, generator=g).to(torch.bfloat16)
     k = torch.randn(TOKENS, HKV, D, generator=g).to(torch.bfloat16)
     v = torch.randn(TOKENS, HKV, D, generator=g).to(torch.bfloat16)
-    hq, hk = H // n_gpus, HKV // n_gpus
-    return (q[:, rank * hq:(rank + 1) * hq].contiguous(),
-            k[:, rank * hk:(rank + 1) * hk].contiguous(),
-            v[:, rank * hk:(rank + 1) * hk].contiguous())
+    from sera_c_b200 import sharding
+    return sharding.slice_heads(q, k, v, rank, n_gpus)
 
 
 def run_ours(args):
@@ -147,6 +145,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     entry.build()
     pkg = entry.load_package()
+    from sera_c_b200 import sharding
     hq, hk = H // n_gpus, HKV // n_gpus
     n_prefix_pages = PREFIX // 16
     num_pages = n_prefix_pages + BRANCHES + 8
@@ -191,8 +190,7 @@ def run_ours(args):
                 works[b].wait()          # out_local[b] is free again (stream wait)
             plan.attention_layer(l, dq_[l], dk_[l], dv_[l], out_local[b])
             if world > 1:
-                works[b] = dist.all_gather_into_tensor(out_full[b].view(-1),
-                                                       out_local[b].view(-1), async_op=True)
+                works[b] = sharding.all_gather_heads(out_local[b], out_full[b], async_op=True)
         for w in works:
             if w is not None:
                 w.wait()

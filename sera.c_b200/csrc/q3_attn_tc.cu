@@ -23,8 +23,8 @@
  *   O += P V    tcgen05.mma, A = P from tensor memory, B = V pages (smem,
  *               MN-major), D = O in tensor memory (fp32).
  *   K/V pages   4 KiB per page per head, fetched by TMA (two 64-column boxes,
- *               128-byte swizzle) straight into the UMMA operand layout. No
- *               multicast: every CTA issues its own loads from local HBM.
+ *               128-byte swizzle) straight into the UMMA operand layout. Every
+ *               CTA issues its own loads, from this GPU's memory only.
  * Warp roles: 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation),
  * 2-5 = softmax of M tile 0, 6-9 = softmax of M tile 1.
  *

@@ -1,5 +1,5 @@
 /* q3_ptx.cuh - thin inline-PTX wrappers for the sm_100a features the attention
- * kernels use: mbarrier, TMA (cp.async.bulk.tensor, no multicast anywhere),
+ * kernels use: mbarrier, TMA (cp.async.bulk.tensor, per-CTA loads only),
  * tensor memory (tcgen05.alloc/ld/st) and the 5th-generation tensor core
  * (tcgen05.mma / tcgen05.commit). Every wait is bounded: after a fixed number
  * of polls it reports failure so the caller can set a status word and leave
