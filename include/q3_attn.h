@@ -371,7 +371,9 @@ bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t layer,
  * tiles) so that every CTA streams the same number of key tiles. This call
  * builds that schedule for a packed batch described by per-token branch and
  * local position (a plain causal sequence: branch 0, lp = absolute position,
- * shared_len 0) and reports it. No counterpart in the reference, whose grid is
+ * shared_len 0) and reports it. `lockstep` selects whole-item waves followed by
+ * a stream-K tail (used when the shared KV would not stay in L2 under the
+ * staggered access of pure stream-K). No counterpart in the reference, whose grid is
  * one warp per (token, head) (ref: src/q3_forward.cu:815-819). */
 typedef struct {
     uint32_t cta;
@@ -392,7 +394,7 @@ typedef struct {
 bool q3_schedule_describe(uint32_t tokens, uint32_t n_kv_heads, uint32_t shared_len,
                           const uint32_t *row_tag, const uint32_t *row_lp,
                           uint32_t pages_per_branch, uint32_t n_branches,
-                          uint32_t num_ctas, uint32_t max_slots,
+                          uint32_t num_ctas, uint32_t max_slots, bool lockstep,
                           q3_sched_summary *summary, q3_sched_segment_info *segments,
                           uint32_t max_segments, char *error, size_t error_len);
 

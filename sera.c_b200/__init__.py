@@ -351,12 +351,13 @@ def pack_suffix_host(items, prefix_len, max_branches, max_suffix):
 
 
 def schedule_describe(row_tag, row_lp, n_kv_heads, shared_len, pages_per_branch,
-                      n_branches, num_ctas, max_slots=1 << 20):
+                      n_branches, num_ctas, max_slots=1 << 20, lockstep=False):
     a, pa = _u32(row_tag)
     b, pb = _u32(row_lp)
     summ = SchedSummary()
     cap = 4 * num_ctas + 4 * ((len(a) + 31) // 32) * n_kv_heads + 16
     segs = (SchedSegmentInfo * cap)()
     _call(lib().q3_schedule_describe, len(a), n_kv_heads, shared_len, pa, pb,
-          pages_per_branch, n_branches, num_ctas, max_slots, ctypes.byref(summ), segs, cap)
+          pages_per_branch, n_branches, num_ctas, max_slots, lockstep, ctypes.byref(summ),
+          segs, cap)
     return summ, [segs[i] for i in range(min(cap, summ.n_segments))]

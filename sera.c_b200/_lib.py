@@ -108,7 +108,7 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
         [vp, vp, vp, u32, vp, vp, vp, vp, u32, vp, u32, u32, u32, vp, vp] + err)
     sig("q3_cuda_qknorm_rope_kvwrite", b, [vp, u32, vp, vp, vp, u32, vp, vp, vp, vp] + err)
     sig("q3_schedule_describe", b,
-        [u32, u32, u32, up, up, u32, u32, u32, u32, ctypes.POINTER(SchedSummary),
+        [u32, u32, u32, up, up, u32, u32, u32, u32, b, ctypes.POINTER(SchedSummary),
          ctypes.POINTER(SchedSegmentInfo), u32] + err)
     sig("q3_attn_version", ctypes.c_char_p, [])
     return L

@@ -26,7 +26,8 @@
  *               128-byte swizzle) straight into the UMMA operand layout. Every
  *               CTA issues its own loads, from this GPU's memory only.
  * Warp roles: 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation),
- * 2-5 = softmax of M tile 0, 6-9 = softmax of M tile 1.
+ * 2-3 idle (register reallocation works on groups of 4 warps), 4-7 = softmax
+ * of M tile 0, 8-11 = softmax of M tile 1.
  *
  * Work is cut stream-K style on the host (q3_sched.h): a CTA receives
  * segments (item, key-tile range). A segment that covers its whole item
@@ -46,7 +47,7 @@ using namespace q3ptx;
 
 namespace {
 
-constexpr uint32_t kThreads = 320;
+constexpr uint32_t kThreads = 384;
 constexpr uint32_t kNQ = 2;              /* M tiles per CTA */
 constexpr uint32_t kStages = 2;          /* K and V ring depth */
 constexpr uint32_t kMetaRing = 4;
@@ -120,6 +121,41 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+/* packed fp32 pairs: one issue slot for two FMAs / adds */
+__device__ __forceinline__ uint64_t pack2(float x, float y) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &x, float &y) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+/* Register budget: setmaxnreg must be executed identically by all four warps
+ * of a warp group. Warps 0-3 (producer, MMA issuer, two idle) give registers
+ * back; the two softmax groups (one S row of 128 fp32 per thread) take them.
+ * 384 threads x 168 at launch = 128 x 40 + 256 x 232. */
+__device__ __forceinline__ void regs_release() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+}
+__device__ __forceinline__ void regs_take() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+}
+
 /* Wait on a barrier unless the CTA is aborting; on expiry raise the abort flag. */
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity,
                                               Misc *misc) {
@@ -171,6 +207,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const uint32_t seg_begin = p.cta_seg_begin[blockIdx.x];
     const uint32_t seg_end = p.cta_seg_begin[blockIdx.x + 1];
 
+    if (warp < 4) regs_release();
     if (warp == 0) {
         /* ===================== TMA producer ===================== */
         if (lane == 0) {
@@ -361,9 +398,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp >= 4) {
         /* ===================== softmax groups ==================== */
-        const uint32_t q = (warp - 2) >> 2;                 /* M tile of this group */
+        regs_take();
+        const uint32_t q = (warp - 4) >> 2;                 /* M tile of this group */
         const uint32_t row = (warp & 3u) * 32u + lane;       /* TMEM lane == tile row */
         const uint32_t lane_addr = ((warp & 3u) * 32u) << 16;
         const uint32_t s_addr = tmem + lane_addr + kColS + q * 128u;
@@ -412,9 +450,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                             if (k2 >= nvis) s[i * 16 + k2] = -INFINITY;
                     }
                 }
-                float mx = s[0];
+                /* row max: 8 independent chains of 3-input max */
+                float mx;
+                {
+                    float mc[8];
 #pragma unroll
-                for (uint32_t i = 1; i < 128; i++) mx = fmaxf(mx, s[i]);
+                    for (uint32_t ch = 0; ch < 8; ch++) {
+                        const float *v = s + ch * 16;
+                        float t = max3(v[0], v[1], v[2]);
+#pragma unroll
+                        for (uint32_t i = 3; i < 15; i += 2) t = max3(t, v[i], v[i + 1]);
+                        mc[ch] = fmaxf(t, v[15]);
+                    }
+                    mx = fmaxf(max3(mc[0], mc[1], mc[2]),
+                               max3(mc[3], mc[4], fmaxf(mc[5], fmaxf(mc[6], mc[7]))));
+                }
 
                 if (j == 0) {
                     m_ref = mx;
@@ -440,16 +490,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 }
                 const float neg = (m_ref == -INFINITY) ? 0.f : -m_ref * c;
                 uint32_t pk[64];
-                float sum = 0.f;
+                {
+                    const uint64_t c2 = pack2(c, c), neg2 = pack2(neg, neg);
+                    uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-                for (uint32_t i = 0; i < 64; i++) {
-                    const float p0 = fast_exp2(fmaf(s[2 * i], c, neg));
-                    const float p1 = fast_exp2(fmaf(s[2 * i + 1], c, neg));
-                    sum += p0 + p1;
-                    const __half2 h = __floats2half2_rn(p0, p1);
-                    pk[i] = *reinterpret_cast<const uint32_t *>(&h);
+                    for (uint32_t i = 0; i < 64; i++) {
+                        float x0, x1;
+                        unpack2(ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, neg2), x0, x1);
+                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        acc[i & 3u] = fadd2(acc[i & 3u], pack2(p0, p1));
+                        const __half2 h = __floats2half2_rn(p0, p1);
+                        pk[i] = *reinterpret_cast<const uint32_t *>(&h);
+                    }
+                    float a0, a1;
+                    unpack2(fadd2(fadd2(acc[0], acc[1]), fadd2(acc[2], acc[3])), a0, a1);
+                    l += a0 + a1;
                 }
-                l += sum;
                 tmem_st32(s_addr, pk);
                 tmem_st32(s_addr + 32u, pk + 32);
                 tmem_wait_st();

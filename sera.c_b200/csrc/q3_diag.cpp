@@ -11,7 +11,8 @@ extern "C" bool q3_schedule_describe(uint32_t tokens, uint32_t n_kv_heads,
                                      uint32_t shared_len, const uint32_t *row_tag,
                                      const uint32_t *row_lp, uint32_t pages_per_branch,
                                      uint32_t n_branches, uint32_t num_ctas,
-                                     uint32_t max_slots, q3_sched_summary *summary,
+                                     uint32_t max_slots, bool lockstep,
+                                     q3_sched_summary *summary,
                                      q3_sched_segment_info *segments,
                                      uint32_t max_segments, char *error,
                                      size_t error_len) {
@@ -26,7 +27,8 @@ extern "C" bool q3_schedule_describe(uint32_t tokens, uint32_t n_kv_heads,
     for (size_t i = 0; i < priv.size(); i++) priv[i] = (uint32_t)(shared.size() + i);
     q3_schedule s;
     if (!q3_build_schedule(s, tokens, n_kv_heads, shared_len, shared, row_tag, row_lp, priv,
-                           pages_per_branch, num_ctas, max_slots, error, error_len))
+                           pages_per_branch, num_ctas, max_slots, lockstep, error,
+                           error_len))
         return false;
     summary->grid = s.grid;
     summary->n_segments = (uint32_t)s.segments.size();

@@ -597,7 +597,8 @@ extern "C" bool q3_prefix_prefill_layer(q3_prefix_kv *prefix, uint32_t layer,
         std::vector<uint32_t> no_shared;
         if (!q3_build_schedule(s, tokens, rt->cfg.n_kv_heads, 0, no_shared, tag.data(),
                                pos.data(), prefix->pages, (uint32_t)prefix->pages.size(),
-                               (uint32_t)rt->num_sms, rt->part_slots, error, error_len))
+                               (uint32_t)rt->num_sms, rt->part_slots, false, error,
+                               error_len))
             return false;
         if (!q3_stage_upload(st, s, pos, dpage, dslot, error, error_len)) return false;
         st->chunk_valid = true;
@@ -818,6 +819,14 @@ extern "C" int64_t q3_pack_suffix_host(const q3_suffix_item *items, uint32_t cou
     return (int64_t)cursor;
 }
 
+/* Staggered stream-K access keeps the shared KV of ALL local heads live at
+ * once; when that exceeds what L2 holds comfortably, walk items in lockstep. */
+static bool q3_prefers_lockstep(const q3_attn_runtime *rt, uint32_t shared_len) {
+    const uint64_t kv_bytes = (uint64_t)((shared_len + Q3_PAGE - 1) / Q3_PAGE) * 2 * 4096 *
+                              rt->cfg.n_kv_heads;
+    return kv_bytes > (48ull << 20);
+}
+
 extern "C" q3_pack_plan *q3_pack_plan_create(q3_prefix_kv *prefix,
                                              q3_branch_set *set,
                                              const q3_suffix_item *items,
@@ -889,7 +898,8 @@ extern "C" q3_pack_plan *q3_pack_plan_create(q3_prefix_kv *prefix,
                            prefix->pages, plan->token_branch.data(),
                            plan->token_local_pos.data(), set->pages,
                            set->pages_per_branch, (uint32_t)rt->num_sms,
-                           rt->part_slots, error, error_len) ||
+                           rt->part_slots, q3_prefers_lockstep(rt, prefix->token_count),
+                           error, error_len) ||
         !q3_stage_upload(plan->stage, s, plan->token_positions, dpage, dslot, error,
                          error_len)) {
         q3_stage_destroy(plan->stage);

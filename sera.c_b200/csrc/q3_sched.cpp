@@ -16,7 +16,8 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
                        const uint32_t *row_tag, const uint32_t *row_lp,
                        const std::vector<uint32_t> &private_table,
                        uint32_t private_stride, uint32_t num_ctas,
-                       uint32_t max_slots, char *error, size_t error_len) {
+                       uint32_t max_slots, bool lockstep, char *error,
+                       size_t error_len) {
     s = q3_schedule();
     if (tokens == 0 || n_kv_heads == 0 || num_ctas == 0)
         return sched_fail(error, error_len, "schedule: empty launch");
@@ -88,55 +89,93 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
     s.grid = grid;
     s.cta_seg_begin.assign(grid + 1, 0);
 
-    /* Stream-K cut: CTA c owns global key tiles [c*total/grid, (c+1)*total/grid). */
-    uint64_t pos = 0; /* global key-tile cursor */
-    uint32_t cta = 0;
-    uint64_t cta_end = total / grid; /* end of CTA 0 */
-    for (uint32_t h = 0; h < n_kv_heads; h++) {
-        for (uint32_t tt = 0; tt < n_tok_tiles; tt++) {
-            const uint32_t n = item_tiles[tt];
+    /* Assignment of key tiles to CTAs.
+     *  - stream-K: CTA c owns global key tiles [c*total/grid, (c+1)*total/grid)
+     *    of the item list; perfect balance, CTAs sit at staggered offsets of
+     *    their items.
+     *  - lockstep waves + stream-K tail (when `lockstep`): the first
+     *    floor(items/grid)*grid items are handed out whole, wave by wave, so
+     *    that all CTAs walk the same key tiles of neighbouring items at the
+     *    same time and share them through L2; only the remaining items are
+     *    cut stream-K style. Chosen by the caller when the shared KV of all
+     *    heads would not stay in L2 under staggered access. */
+    struct Item { uint32_t h, tt, n; };
+    std::vector<Item> items;
+    items.reserve((size_t)n_kv_heads * n_tok_tiles);
+    for (uint32_t h = 0; h < n_kv_heads; h++)
+        for (uint32_t tt = 0; tt < n_tok_tiles; tt++)
+            items.push_back(Item{h, tt, item_tiles[tt]});
+    struct Piece { uint32_t item, begin, end; };
+    std::vector<std::vector<Piece>> per_cta(grid);
+    size_t first_tail = 0;
+    if (lockstep && items.size() >= grid) {
+        const size_t waves = items.size() / grid;
+        for (size_t w = 0; w < waves; w++)
+            for (uint32_t c = 0; c < grid; c++) {
+                const uint32_t i = (uint32_t)(w * grid + c);
+                per_cta[c].push_back(Piece{i, 0, items[i].n});
+            }
+        first_tail = waves * grid;
+    }
+    {
+        uint64_t tail_total = 0;
+        for (size_t i = first_tail; i < items.size(); i++) tail_total += items[i].n;
+        uint64_t pos = 0;
+        uint32_t cta = 0;
+        uint64_t cta_end = tail_total / grid;
+        for (size_t i = first_tail; i < items.size(); i++) {
             uint32_t done = 0;
-            const size_t first_seg = s.segments.size();
-            while (done < n) {
+            while (done < items[i].n) {
                 while (pos >= cta_end && cta + 1 < grid) {
                     cta++;
-                    s.cta_seg_begin[cta] = (uint32_t)s.segments.size();
-                    cta_end = (uint64_t)(cta + 1) * total / grid;
+                    cta_end = (uint64_t)(cta + 1) * tail_total / grid;
                 }
                 const uint32_t take =
-                    (uint32_t)std::min<uint64_t>(n - done, cta_end - pos);
-                q3_segment seg;
-                seg.tok0 = tt * Q3_TOK_TILE;
-                seg.kv_head = h;
-                seg.tile_begin = done;
-                seg.tile_end = done + take;
-                seg.shared_tiles = shared_tiles;
-                seg.partial_slot = -1;
-                seg.run_begin = s.tile_run_begin[tt];
-                seg.run_end = s.tile_run_begin[tt + 1];
-                s.segments.push_back(seg);
+                    (uint32_t)std::min<uint64_t>(items[i].n - done, cta_end - pos);
+                per_cta[cta].push_back(Piece{(uint32_t)i, done, done + take});
                 done += take;
                 pos += take;
             }
-            const uint32_t n_seg = (uint32_t)(s.segments.size() - first_seg);
-            if (n_seg > 1) {
-                if (s.n_slots + n_seg > max_slots)
-                    return sched_fail(error, error_len,
-                                      "schedule: out of partial slots");
-                q3_merge_item m;
-                m.tok0 = tt * Q3_TOK_TILE;
-                m.kv_head = h;
-                m.slot_begin = s.n_slots;
-                m.slot_count = n_seg;
-                for (uint32_t i = 0; i < n_seg; i++)
-                    s.segments[first_seg + i].partial_slot = (int32_t)(s.n_slots + i);
-                s.n_slots += n_seg;
-                s.merges.push_back(m);
-            }
         }
     }
-    for (uint32_t c = cta + 1; c <= grid; c++)
+    /* Flatten; cut items get consecutive partial slots and a merge entry. */
+    std::vector<uint32_t> item_pieces(items.size(), 0), item_slot(items.size(), 0);
+    for (uint32_t c = 0; c < grid; c++)
+        for (const Piece &pc : per_cta[c]) item_pieces[pc.item]++;
+    for (size_t i = 0; i < items.size(); i++) {
+        if (item_pieces[i] > 1) {
+            if (s.n_slots + item_pieces[i] > max_slots)
+                return sched_fail(error, error_len, "schedule: out of partial slots");
+            q3_merge_item m;
+            m.tok0 = items[i].tt * Q3_TOK_TILE;
+            m.kv_head = items[i].h;
+            m.slot_begin = s.n_slots;
+            m.slot_count = item_pieces[i];
+            item_slot[i] = s.n_slots;
+            s.n_slots += item_pieces[i];
+            s.merges.push_back(m);
+        }
+    }
+    std::vector<uint32_t> item_next(items.size(), 0);
+    for (uint32_t c = 0; c < grid; c++) {
         s.cta_seg_begin[c] = (uint32_t)s.segments.size();
+        for (const Piece &pc : per_cta[c]) {
+            const Item &it = items[pc.item];
+            q3_segment seg;
+            seg.tok0 = it.tt * Q3_TOK_TILE;
+            seg.kv_head = it.h;
+            seg.tile_begin = pc.begin;
+            seg.tile_end = pc.end;
+            seg.shared_tiles = shared_tiles;
+            seg.partial_slot = item_pieces[pc.item] > 1
+                                   ? (int32_t)(item_slot[pc.item] + item_next[pc.item]++)
+                                   : -1;
+            seg.run_begin = s.tile_run_begin[it.tt];
+            seg.run_end = s.tile_run_begin[it.tt + 1];
+            s.segments.push_back(seg);
+        }
+    }
+    s.cta_seg_begin[grid] = (uint32_t)s.segments.size();
     return true;
 }
 

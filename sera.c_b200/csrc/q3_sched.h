@@ -81,6 +81,7 @@ struct q3_schedule {
  *                    entries
  *   num_ctas         CTAs the launch may use (SM count)
  *   max_slots        partial slots available
+ *   lockstep         hand out whole items in waves first (see q3_sched.cpp)
  * Returns false with a message on an inconsistent description. */
 bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
                        uint32_t shared_len,
@@ -88,7 +89,8 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
                        const uint32_t *row_tag, const uint32_t *row_lp,
                        const std::vector<uint32_t> &private_table,
                        uint32_t private_stride, uint32_t num_ctas,
-                       uint32_t max_slots, char *error, size_t error_len);
+                       uint32_t max_slots, bool lockstep, char *error,
+                       size_t error_len);
 
 /* Decode: cut every sequence into chunks of `chunk_pages` pages. */
 void q3_build_decode_work(const uint32_t *ctx_lens, uint32_t num_seqs,

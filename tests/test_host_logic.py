@@ -70,8 +70,10 @@ def test_pack_suffix_rejects(pkg, items, msg):
         pkg.pack_suffix_host(items, prefix_len=10, max_branches=8, max_suffix=16)
 
 
-def _check_schedule(pkg, row_tag, row_lp, n_kv, shared_len, ppb, nb, ctas):
-    summ, segs = pkg.schedule_describe(row_tag, row_lp, n_kv, shared_len, ppb, nb, ctas)
+def _check_schedule(pkg, row_tag, row_lp, n_kv, shared_len, ppb, nb, ctas, lockstep=False,
+                    balanced=True):
+    summ, segs = pkg.schedule_describe(row_tag, row_lp, n_kv, shared_len, ppb, nb, ctas,
+                                       lockstep=lockstep)
     assert summ.n_segments == len(segs)
     T = len(row_tag)
     n_tt = (T + 31) // 32
@@ -110,7 +112,8 @@ def _check_schedule(pkg, row_tag, row_lp, n_kv, shared_len, ppb, nb, ctas):
     assert summ.n_merges == n_cut and summ.n_slots == len(slots)
     loads = list(per_cta.values())
     assert len(loads) == summ.grid == min(ctas, summ.total_key_tiles)
-    assert max(loads) - min(loads) <= 1              # stream-K balance
+    if balanced:
+        assert max(loads) - min(loads) <= 1          # stream-K balance
     return summ
 
 
@@ -127,6 +130,10 @@ def test_schedule_cascade_configs(pkg):
         tag = np.repeat(np.arange(B, dtype=np.uint32), n)
         lp = np.tile(np.arange(n, dtype=np.uint32), B)
         _check_schedule(pkg, tag, lp, 8, P, (n + 15) // 16, B, 148)
+        # whole-item waves + stream-K tail: same coverage, same balance (equal items),
+        # and no more cut items than CTAs
+        s = _check_schedule(pkg, tag, lp, 8, P, (n + 15) // 16, B, 148, lockstep=True)
+        assert s.n_merges <= 148
 
 
 def test_schedule_ragged_and_tiny(pkg):
@@ -137,6 +144,7 @@ def test_schedule_ragged_and_tiny(pkg):
     lp = np.concatenate([np.arange(n, dtype=np.uint32) for n in lens])
     _check_schedule(pkg, tag, lp, 2, 77, 5, 16, 148)
     _check_schedule(pkg, tag, lp, 1, 0, 5, 16, 7)
+    _check_schedule(pkg, tag, lp, 2, 77, 5, 16, 5, lockstep=True, balanced=False)
     _check_schedule(pkg, np.zeros(1, np.uint32), np.zeros(1, np.uint32), 1, 0, 1, 1, 148)
 
 
