@@ -145,6 +145,33 @@ __device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
     asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+/* 2^x for a pair without the special-function unit: round-to-nearest split
+ * x = n + r, r in [-0.5, 0.5], cubic minimax for 2^r (relative error 7.5e-5,
+ * below the f16 rounding of P), n added into the exponent field. The MUFU
+ * executes 16 ex2 per clock per SM, exactly as many as the tensor core consumes
+ * at full rate; moving a share of them to the FMA pipe takes it off the
+ * critical path. Inputs must be finite and >= -126. */
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float &p0, float &p1) {
+    const uint64_t magic = pack2(12582912.0f, 12582912.0f);       /* 1.5 * 2^23 */
+    const uint64_t neg_magic = pack2(-12582912.0f, -12582912.0f);
+    const uint64_t minus1 = pack2(-1.0f, -1.0f);
+    const uint64_t xr = fadd2(x2, magic);                 /* n in the low mantissa bits */
+    const uint64_t n = fadd2(xr, neg_magic);
+    const uint64_t r = ffma2(n, minus1, x2);              /* r = x - n */
+    uint64_t p = ffma2(r, pack2(0.055170901f, 0.055170901f), pack2(0.24260952f, 0.24260952f));
+    p = ffma2(r, p, pack2(0.69326097f, 0.69326097f));
+    p = ffma2(r, p, pack2(0.99992818f, 0.99992818f));
+    float xr0, xr1, q0, q1;
+    unpack2(xr, xr0, xr1);
+    unpack2(p, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(xr0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(xr1) << 23));
+}
+/* pairs out of every 8 whose exponentials go through exp2_poly2 */
+#ifndef Q3_POLY_PAIRS_OF_8
+#define Q3_POLY_PAIRS_OF_8 1
+#endif
+
 /* Register budget: setmaxnreg must be executed identically by all four warps
  * of a warp group. Warps 0-3 (producer, MMA issuer, two idle) give registers
  * back; the two softmax groups (one S row of 128 fp32 per thread) take them.
@@ -495,9 +522,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                     for (uint32_t i = 0; i < 64; i++) {
-                        float x0, x1;
-                        unpack2(ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, neg2), x0, x1);
-                        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                        float x0, x1, p0, p1;
+                        const uint64_t x2 = ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, neg2);
+                        unpack2(x2, x0, x1);
+                        if ((i & 7u) < Q3_POLY_PAIRS_OF_8) {
+                            exp2_poly2(pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f)), p0, p1);
+                        } else {
+                            p0 = fast_exp2(x0);
+                            p1 = fast_exp2(x1);
+                        }
                         acc[i & 3u] = fadd2(acc[i & 3u], pack2(p0, p1));
                         const __half2 h = __floats2half2_rn(p0, p1);
                         pk[i] = *reinterpret_cast<const uint32_t *>(&h);
