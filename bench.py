@@ -205,7 +205,7 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, drain=None):
         with torch.cuda.stream(stream):
             for _ in range(warmup):
                 fn()
@@ -217,6 +217,8 @@ def run_ours(args):
             e0.record(stream)
             for _ in range(steps):
                 fn()
+            if drain:
+                drain()          # copy-out streams: the last result must be on the host
             e1.record(stream)
             barrier()
             ms = e0.elapsed_time(e1)
@@ -234,7 +236,7 @@ def run_ours(args):
         sampler.start()
     ms, phases, launches = timed(step_device, args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
-    ms_e2e, _, _ = timed(step_host, max(1, min(args.steps, 3)), 1)
+    ms_e2e, _, _ = timed(step_host, max(1, min(args.steps, 3)), 1, drain=rt.synchronize)
     e2e_steps = max(1, min(args.steps, 3))
     rt.synchronize()
     status = rt.stats().device_status

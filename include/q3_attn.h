@@ -356,10 +356,12 @@ bool q3_cuda_qknorm_rope_kvwrite(q3_attn_runtime *rt, uint32_t layer,
                                  const uint32_t *dst_slot, void *q_out,
                                  char *error, size_t error_len);
 
-/* Host-buffer entry for callers whose activations live in host memory: copies
- * q/k/v in (pinned staging if the pointers are not pinned), runs
- * q3_suffix_attention_layer, copies `out` back, all on the runtime's stream.
- * Does not synchronise. */
+/* Host-buffer entry for callers whose activations live in (pinned) host
+ * memory: copies q/k/v in, runs q3_suffix_attention_layer, copies `out` back.
+ * Successive calls are pipelined over three device slots and two copy streams,
+ * so the copy-in of the next layer and the copy-out of the previous one overlap
+ * the kernels. Does not synchronise: `out_host` is valid, and q/k/v may be
+ * reused, after q3_attn_synchronize. */
 bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t layer,
                                     const void *q_host, const void *k_host,
                                     const void *v_host, void *out_host,

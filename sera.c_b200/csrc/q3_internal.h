@@ -86,7 +86,12 @@ struct q3_attn_runtime {
     void *host_stage;
     size_t host_stage_bytes;
     void *dev_stage;
-    size_t dev_stage_bytes;
+    size_t dev_stage_bytes;      /* per slot */
+    /* the host-buffer entry pipelines three slots over two copy streams */
+    cudaStream_t h2d_stream, d2h_stream;
+    cudaEvent_t ev_in[3], ev_compute[3], ev_out[3];
+    bool copy_ready;
+    uint64_t host_calls;
 
     uint64_t n_alloc, n_free, n_sync, n_launch;
     uint64_t workspace_bytes;

@@ -165,6 +165,9 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     rt->status_host = nullptr;
     rt->host_stage = rt->dev_stage = nullptr;
     rt->host_stage_bytes = rt->dev_stage_bytes = 0;
+    rt->h2d_stream = rt->d2h_stream = nullptr;
+    rt->copy_ready = false;
+    rt->host_calls = 0;
     rt->n_alloc = rt->n_free = rt->n_sync = rt->n_launch = 0;
     rt->workspace_bytes = 0;
     rt->timing_on = false;
@@ -261,6 +264,17 @@ extern "C" void q3_attn_destroy(q3_attn_runtime *rt) {
     rt_free(rt, rt->status_dev);
     rt_free(rt, rt->dev_stage);
     for (cudaEvent_t e : rt->ev) cudaEventDestroy(e);
+    if (rt->copy_ready) {
+        cudaStreamSynchronize(rt->h2d_stream);
+        cudaStreamSynchronize(rt->d2h_stream);
+        for (int i = 0; i < 3; i++) {
+            cudaEventDestroy(rt->ev_in[i]);
+            cudaEventDestroy(rt->ev_compute[i]);
+            cudaEventDestroy(rt->ev_out[i]);
+        }
+        cudaStreamDestroy(rt->h2d_stream);
+        cudaStreamDestroy(rt->d2h_stream);
+    }
     if (rt->host_stage) cudaFreeHost(rt->host_stage);
     if (rt->status_host) cudaFreeHost(rt->status_host);
     if (rt->stream) cudaStreamDestroy(rt->stream);
@@ -297,6 +311,7 @@ extern "C" bool q3_attn_synchronize(q3_attn_runtime *rt, char *error,
     cudaMemcpyAsync(rt->status_host, rt->status_dev, sizeof(uint32_t),
                     cudaMemcpyDeviceToHost, rt->stream);
     cudaError_t e = cudaStreamSynchronize(rt->stream);
+    if (e == cudaSuccess && rt->copy_ready) e = cudaStreamSynchronize(rt->d2h_stream);
     rt->n_sync++;
     if (e != cudaSuccess)
         return q3_fail_cuda(error, error_len, "q3_attn_synchronize", e);
@@ -982,29 +997,60 @@ extern "C" bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t laye
     const size_t qb = (size_t)plan->tokens * rt->cfg.n_heads * Q3_D * 2;
     const size_t kb = (size_t)plan->tokens * rt->cfg.n_kv_heads * Q3_D * 2;
     const size_t ob = rt->cfg.out_fp32 ? 2 * qb : qb;
-    const size_t need = qb + ob + 2 * kb;
+    const size_t need = (qb + ob + 2 * kb + 255) & ~(size_t)255;
+    if (!rt->copy_ready) {
+        /* set-up, once: two copy streams and the events that order the slots */
+        bool ok = cudaStreamCreateWithFlags(&rt->h2d_stream, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&rt->d2h_stream, cudaStreamNonBlocking) == cudaSuccess;
+        for (int i = 0; i < 3 && ok; i++)
+            ok = cudaEventCreateWithFlags(&rt->ev_in[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&rt->ev_compute[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&rt->ev_out[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok)
+            return q3_fail(error, error_len,
+                           "q3_suffix_attention_layer_host: stream set-up failed");
+        rt->copy_ready = true;
+    }
     if (need > rt->dev_stage_bytes) {
         cudaStreamSynchronize(rt->stream);
+        cudaStreamSynchronize(rt->h2d_stream);
+        cudaStreamSynchronize(rt->d2h_stream);
         rt_free(rt, rt->dev_stage);
         rt->dev_stage = nullptr;
         rt->dev_stage_bytes = 0;
-        if (rt_malloc(rt, &rt->dev_stage, need) != cudaSuccess)
+        if (rt_malloc(rt, &rt->dev_stage, 3 * need) != cudaSuccess)
             return q3_fail(error, error_len,
                            "q3_suffix_attention_layer_host: allocation failed");
         rt->dev_stage_bytes = need;
+        rt->host_calls = 0;
     }
-    uint8_t *d = (uint8_t *)rt->dev_stage;
+    /* Slot i%3: copy-in (h2d stream) -> kernels (runtime stream) -> copy-out
+     * (d2h stream). The copy-in of call i+1 and the copy-out of call i-1 run
+     * while call i computes. A slot is reused only after its copy-out. */
+    const uint32_t slot = (uint32_t)(rt->host_calls % 3);
+    const bool reused = rt->host_calls >= 3;
+    rt->host_calls++;
+    uint8_t *d = (uint8_t *)rt->dev_stage + (size_t)slot * rt->dev_stage_bytes;
     void *dq = d, *dk = d + qb, *dv = d + qb + kb, *dout = d + qb + 2 * kb;
-    cudaError_t e = cudaMemcpyAsync(dq, q_host, qb, cudaMemcpyHostToDevice, rt->stream);
+    cudaError_t e = cudaSuccess;
+    if (reused) e = cudaStreamWaitEvent(rt->h2d_stream, rt->ev_out[slot], 0);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(dk, k_host, kb, cudaMemcpyHostToDevice, rt->stream);
+        e = cudaMemcpyAsync(dq, q_host, qb, cudaMemcpyHostToDevice, rt->h2d_stream);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(dv, v_host, kb, cudaMemcpyHostToDevice, rt->stream);
+        e = cudaMemcpyAsync(dk, k_host, kb, cudaMemcpyHostToDevice, rt->h2d_stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(dv, v_host, kb, cudaMemcpyHostToDevice, rt->h2d_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev_in[slot], rt->h2d_stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(rt->stream, rt->ev_in[slot], 0);
     if (e != cudaSuccess)
         return q3_fail_cuda(error, error_len, "q3_suffix_attention_layer_host: H2D", e);
     if (!q3_suffix_attention_layer(plan, layer, dq, dk, dv, dout, error, error_len))
         return false;
-    e = cudaMemcpyAsync(out_host, dout, ob, cudaMemcpyDeviceToHost, rt->stream);
+    e = cudaEventRecord(rt->ev_compute[slot], rt->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(rt->d2h_stream, rt->ev_compute[slot], 0);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(out_host, dout, ob, cudaMemcpyDeviceToHost, rt->d2h_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(rt->ev_out[slot], rt->d2h_stream);
     if (e != cudaSuccess)
         return q3_fail_cuda(error, error_len, "q3_suffix_attention_layer_host: D2H", e);
     return true;

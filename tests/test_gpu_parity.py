@@ -196,6 +196,38 @@ def test_warm_path_counters(pkg):
     rt.close()
 
 
+def test_host_buffer_entry_pipelined(pkg):
+    """q3_suffix_attention_layer_host: five back-to-back calls (three staging
+    slots, so slots are reused) give the same rows as the device entry."""
+    case = harness.rounded_case(_cases.make_case("ragged"))
+    _, rt, prefix, bset, plan = harness.run_case_native(pkg, case, return_runtime=True)
+    P, S = case.P, case.S
+    g = torch.Generator().manual_seed(3)
+    outs_dev, outs_host, keep = [], [], []
+    for i in range(5):
+        q = torch.randn(S, case.H, case.D, generator=g).to(torch.bfloat16)
+        k = torch.randn(S, case.Hkv, case.D, generator=g).to(torch.bfloat16)
+        v = torch.randn(S, case.Hkv, case.D, generator=g).to(torch.bfloat16)
+        od = torch.zeros(S, case.H, case.D, dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        plan.attention_layer(i % 2, q.cuda(), k.cuda(), v.cuda(), od)
+        rt.synchronize()
+        outs_dev.append(od.cpu())
+        keep.append((q.pin_memory(), k.pin_memory(), v.pin_memory(),
+                     torch.zeros(S, case.H, case.D, dtype=torch.bfloat16).pin_memory()))
+    s0 = rt.stats()
+    for i, (q, k, v, oh) in enumerate(keep):
+        plan.attention_layer_host(i % 2, q, k, v, oh)
+    rt.synchronize()
+    for i, (_, _, _, oh) in enumerate(keep):
+        assert torch.equal(oh, outs_dev[i]), i
+    s1 = rt.stats()
+    assert s1.host_syncs == s0.host_syncs + 1      # only the explicit synchronize
+    for o in (plan, bset, prefix):
+        o.close()
+    rt.close()
+
+
 def test_error_paths(pkg):
     rt = pkg.Runtime(num_layers=1, n_heads=8, n_kv_heads=1, max_positions=256,
                      max_tokens=32, num_pages=12)
