@@ -5,6 +5,11 @@
 
 #include <algorithm>
 
+/* start-up cost of a segment, in quarter key tiles */
+#ifndef Q3_SCHED_SEGMENT_COST
+#define Q3_SCHED_SEGMENT_COST 8
+#endif
+
 static bool sched_fail(char *error, size_t error_len, const char *msg) {
     if (error && error_len) snprintf(error, error_len, "%s", msg);
     return false;
@@ -118,23 +123,33 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
         first_tail = waves * grid;
     }
     {
-        uint64_t tail_total = 0;
-        for (size_t i = first_tail; i < items.size(); i++) tail_total += items[i].n;
-        uint64_t pos = 0;
+        /* Cost-balanced stream-K over items [first_tail, end): a segment costs
+         * its key tiles plus a fixed start-up (Q load, pipeline fill, epilogue),
+         * so a CTA that receives many short items gets fewer tiles. Costs are
+         * in quarter tiles. */
+        const uint64_t F = Q3_SCHED_SEGMENT_COST;
+        uint64_t rem = 0;   /* cost not yet handed out */
+        for (size_t i = first_tail; i < items.size(); i++) rem += 4ull * items[i].n + F;
+        rem += (uint64_t)(grid - 1) * F;   /* every CTA boundary cuts one item: its
+                                              continuation pays the start-up again */
         uint32_t cta = 0;
-        uint64_t cta_end = tail_total / grid;
+        uint64_t budget = rem / grid, used = 0;
         for (size_t i = first_tail; i < items.size(); i++) {
             uint32_t done = 0;
             while (done < items[i].n) {
-                while (pos >= cta_end && cta + 1 < grid) {
-                    cta++;
-                    cta_end = (uint64_t)(cta + 1) * tail_total / grid;
+                if (cta + 1 < grid && used + F + 4 > budget) {
+                    cta++;                        /* re-balance over what is left */
+                    budget = rem / (grid - cta);
+                    used = 0;
                 }
-                const uint32_t take =
-                    (uint32_t)std::min<uint64_t>(items[i].n - done, cta_end - pos);
+                uint32_t take = items[i].n - done;
+                if (cta + 1 < grid && budget > used + F)
+                    take = (uint32_t)std::min<uint64_t>(take,
+                                                        std::max<uint64_t>(1, (budget - used - F) / 4));
                 per_cta[cta].push_back(Piece{(uint32_t)i, done, done + take});
                 done += take;
-                pos += take;
+                used += F + 4ull * take;
+                rem -= std::min<uint64_t>(rem, F + 4ull * take);
             }
         }
     }
