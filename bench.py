@@ -182,14 +182,31 @@ def run_ours(args):
     out_host = torch.zeros(TOKENS, hq, D, dtype=torch.bfloat16).pin_memory()
     stream = rt.torch_stream()
 
+    fused = world > 1 and args.gather == "fused"
+    pg = sharding.PeerGather(TOKENS, hq, D, torch.bfloat16, device) if fused else None
+    seq_base = [0]
+
     def step_device():
+        if fused:
+            # attention kernels store their rows into every rank's gathered
+            # buffer; buffer b is reused by layer l+2 only after every rank
+            # has seen layer l complete (device-side flag wait, no collective)
+            s0 = seq_base[0]
+            for l in range(L):
+                if l >= 2:
+                    rt.wait_gathered(pg.peers(l), s0 + l - 1)
+                plan.attention_layer_gathered(l, dq_[l], dk_[l], dv_[l], pg.peers(l), s0 + l + 1)
+            rt.wait_gathered(pg.peers(L - 2), s0 + L - 1)
+            rt.wait_gathered(pg.peers(L - 1), s0 + L)
+            seq_base[0] = s0 + L
+            return
         works = [None, None]
         for l in range(L):
             b = l & 1
             if works[b] is not None:
                 works[b].wait()          # out_local[b] is free again (stream wait)
             plan.attention_layer(l, dq_[l], dk_[l], dv_[l], out_local[b])
-            if world > 1:
+            if world > 1 and args.gather == "nccl":
                 works[b] = sharding.all_gather_heads(out_local[b], out_full[b], async_op=True)
         for w in works:
             if w is not None:
@@ -263,7 +280,8 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "layers": L, "prefix_tokens": PREFIX,
                        "branches": BRANCHES, "suffix_tokens_per_branch": SUFFIX,
                        "heads": "%d/%d x %d" % (H, HKV, D), "kv": "paged f16, page 16, permuted table",
-                       "sharding": "kv_heads/%d + all-gather per layer" % n_gpus,
+                       "sharding": "kv_heads/%d + all-gather per layer (%s)" % (
+                           n_gpus, args.gather if n_gpus > 1 else "single GPU"),
                        "l2": "inputs larger than L2 (8.6 GB of KV per step)"},
             "tflops": FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12,
             "e2e": {"value": TOKENS / (e2e_ms_per_step * 1e-3), "unit": UNIT,
@@ -341,14 +359,14 @@ def case_prefill(pkg, torch, device, T=4096, reps=20):
     return res
 
 
-def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20):
+def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20, n_kv_heads=HKV):
     """Shared-prefix + packed-suffix attention, one layer, prefix resident."""
     peaks = measured_peaks()
     g = torch.Generator(device=device).manual_seed(0)
     rnd = lambda *shape: torch.randn(*shape, generator=g, device=device).to(torch.bfloat16)
     S = B * n
     ppb = (n + 15) // 16
-    rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=P + n + 8,
+    rt = pkg.Runtime(num_layers=1, n_heads=8 * n_kv_heads, n_kv_heads=n_kv_heads, max_positions=P + n + 8,
                      max_tokens=S, num_pages=P // 16 + ppb * B + 4, device=device.index)
     rt.enable_timing(16 * reps + 64)
     prefix = pkg.Prefix(rt, P)
@@ -359,12 +377,12 @@ def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20):
     prefix.seal()
     bset = pkg.BranchSet(prefix, B, n)
     plan = pkg.PackPlan(prefix, bset, [(bset.acquire(), n) for _ in range(B)])
-    q, k, v = rnd(S, H, D), rnd(S, HKV, D), rnd(S, HKV, D)
-    out = torch.zeros(S, H, D, dtype=torch.bfloat16, device=device)
+    q, k, v = rnd(S, 8 * n_kv_heads, D), rnd(S, n_kv_heads, D), rnd(S, n_kv_heads, D)
+    out = torch.zeros(S, 8 * n_kv_heads, D, dtype=torch.bfloat16, device=device)
     ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, k, v, out), reps)
-    flops = 4 * D * H * (S * P + B * n * (n + 1) // 2)
+    flops = 4 * D * 8 * n_kv_heads * (S * P + B * n * (n + 1) // 2)
     k_ms = ph["attention"][0] / max(ph["attention"][1], 1)
-    res = {"prefix": P, "branches": B, "suffix": n, "ms": ms,
+    res = {"prefix": P, "branches": B, "suffix": n, "kv_heads": n_kv_heads, "ms": ms,
            "suffix_tokens_per_s": S / ms * 1e3, "tflops": flops / ms / 1e9,
            "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
            "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
@@ -412,6 +430,7 @@ CASES = {
     "prefill_4096": lambda pkg, torch, dev, reps: case_prefill(pkg, torch, dev, 4096, reps),
     "cascade_p8192_b64x24": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, 8192, 64, 24, reps),
     "stack_layer_p32768_b128x16": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, PREFIX, BRANCHES, SUFFIX, reps),
+    "stack_layer_1kvhead": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, PREFIX, BRANCHES, SUFFIX, reps, 1),
     "decode_256seq": lambda pkg, torch, dev, reps: case_decode(pkg, torch, dev, 256, reps),
     "decode_64seq": lambda pkg, torch, dev, reps: case_decode(pkg, torch, dev, 64, reps),
 }
@@ -521,6 +540,10 @@ def main():
                     help="skip the single-layer prefill / cascade / decode lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
+                    help="per-layer output all-gather at N > 1: 'fused' = peer stores from "
+                         "the attention epilogue (default), 'nccl' = all_gather_into_tensor "
+                         "overlapped on a side stream, 'none' = skipped (diagnostic)")
     ap.add_argument("--case", choices=sorted(CASES), default=None,
                     help="run only this single-layer case (for profiler captures)")
     ap.add_argument("--reps", type=int, default=5)

@@ -282,6 +282,33 @@ bool q3_suffix_attention_layer(q3_pack_plan *plan, uint32_t layer,
                                const void *q, const void *k, const void *v,
                                void *out, char *error, size_t error_len);
 
+/* --- head-sharded runs: attention fused with the output all-gather ------ *
+ * New (the reference is single-device). With the KV heads sharded over the
+ * GPUs of one box, every rank needs all heads' outputs after a layer. Instead
+ * of a separate collective, the attention and merge kernels store each output
+ * row into the gathered buffer of every rank: `gathered[r]` is the base of rank
+ * r's buffer [n_ranks][tokens][n_heads][128] (bf16, or fp32 with out_fp32),
+ * mapped into this process (peer memory over NVLink); this rank fills slot
+ * `rank` of each. `flags[r]` is rank r's array of n_ranks uint32 (also peer
+ * mapped, zero-initialised): after the layer's stores, `seq` is published in
+ * flags[r][rank] for every r. q3_attn_wait_gathered queues a bounded
+ * device-side wait until this rank's flags all reached `seq`, i.e. its
+ * gathered buffer holds that layer from every rank (timeout: status bit 2,
+ * reported by q3_attn_synchronize). seq must increase; comparisons wrap. */
+#define Q3_MAX_GATHER_RANKS 8u
+typedef struct {
+    uint32_t n_ranks;
+    uint32_t rank;
+    void *gathered[Q3_MAX_GATHER_RANKS];
+    uint32_t *flags[Q3_MAX_GATHER_RANKS];
+} q3_gather_peers;
+bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t layer,
+                                        const void *q, const void *k, const void *v,
+                                        const q3_gather_peers *gather, uint32_t seq,
+                                        char *error, size_t error_len);
+bool q3_attn_wait_gathered(q3_attn_runtime *rt, const q3_gather_peers *gather,
+                           uint32_t seq, char *error, size_t error_len);
+
 /* --- paged decode: many independent sequences, one query token each --- */
 typedef struct q3_decode_plan q3_decode_plan;
 /* Host arrays: ctx_lens[num_seqs]; CSR page lists page_indptr[num_seqs+1],

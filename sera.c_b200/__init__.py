@@ -13,7 +13,7 @@ import os
 
 import numpy as np
 
-from ._lib import ERRLEN, Q3Error, bind, lib_path  # noqa: F401
+from ._lib import ERRLEN, GatherPeers, Q3Error, bind, lib_path  # noqa: F401
 
 PAGE = 16
 D = 128
@@ -155,6 +155,9 @@ class Runtime:
         _call(lib().q3_attn_phase_times, self.h, ms, n)
         return {name: (ms[i], int(n[i])) for i, name in enumerate(self.PHASES)}
 
+    def wait_gathered(self, peers, seq):
+        _call(lib().q3_attn_wait_gathered, self.h, ctypes.byref(peers), seq)
+
     def alloc_pages(self, n):
         out = np.empty(n, np.uint32)
         _call(lib().q3_pages_alloc, self.h, n, out.ctypes.data_as(_c_u32p))
@@ -284,6 +287,12 @@ class PackPlan:
     def attention_layer(self, layer, q, k, v, out):
         _call(lib().q3_suffix_attention_layer, self.h, layer, _ptr(q), _ptr(k), _ptr(v),
               _ptr(out))
+
+    def attention_layer_gathered(self, layer, q, k, v, peers, seq):
+        """Attention fused with the output all-gather: `peers` is a GatherPeers
+        (see sharding.PeerGather)."""
+        _call(lib().q3_suffix_attention_layer_gathered, self.h, layer, _ptr(q), _ptr(k),
+              _ptr(v), ctypes.byref(peers), seq)
 
     def attention_layer_host(self, layer, q, k, v, out):
         """q/k/v/out: pinned host torch tensors."""

@@ -14,6 +14,11 @@ def lib_path():
     return os.path.join(PKG, "libq3attn.so")
 
 
+class GatherPeers(ctypes.Structure):
+    _fields_ = [("n_ranks", ctypes.c_uint32), ("rank", ctypes.c_uint32),
+                ("gathered", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8)]
+
+
 def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     path = lib_path()
     if not os.path.exists(path):
@@ -100,6 +105,9 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     sig("q3_pack_plan_branch_offsets", up, [vp])
     sig("q3_suffix_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)
     sig("q3_suffix_attention_layer_host", b, [vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_suffix_attention_layer_gathered", b,
+        [vp, u32, vp, vp, vp, ctypes.POINTER(GatherPeers), u32] + err)
+    sig("q3_attn_wait_gathered", b, [vp, ctypes.POINTER(GatherPeers), u32] + err)
     sig("q3_decode_plan_create", vp, [vp, up, up, up, u32] + err)
     sig("q3_decode_plan_destroy", None, [vp])
     sig("q3_decode_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)

@@ -31,8 +31,13 @@
  *
  * Work is cut stream-K style on the host (q3_sched.h): a CTA receives
  * segments (item, key-tile range). A segment that covers its whole item
- * writes bf16 output; otherwise it writes un-normalised fp32 partials plus
- * (max, sum) and merge_partials_kernel combines them with log-sum-exp.
+ * writes the output rows; a piece of a cut item writes un-normalised fp32
+ * partials plus (max, sum) and bumps an arrival counter per 32 rows; the warp
+ * that arrives last combines all pieces of its rows with log-sum-exp (its own
+ * partial straight from tensor memory) and writes them. No CTA waits for
+ * another. In head-sharded runs the rows are also stored
+ * into the other GPUs' gathered buffers (peer memory), so the per-layer
+ * all-gather is part of this kernel.
  *
  * Every mbarrier wait is bounded; on expiry the thread raises a flag in shared
  * memory, the status word is set and all roles drain and leave.
@@ -93,6 +98,19 @@ struct Misc {
     TileMeta meta[kMetaRing];
 };
 
+/* Head-sharded runs: the same output rows are also stored into the gathered
+ * buffers of the other GPUs of the box (plain stores to peer-mapped memory
+ * over NVLink), which makes the per-layer all-gather part of the epilogue
+ * instead of a separate collective that would compete for SMs. */
+struct OutPeers {
+    void *ptr[Q3_MAX_GATHER_RANKS];
+    uint32_t n;
+};
+struct GatherFlags {
+    uint32_t *ptr[Q3_MAX_GATHER_RANKS];
+    uint32_t n;
+};
+
 struct AttnParams {
     const uint32_t *page_ids;
     const q3_run *runs;
@@ -110,8 +128,10 @@ struct AttnParams {
     float scale_log2;           /* scale * log2(e) */
     uint32_t out_fp32;
     void *out;                  /* [tokens][n_heads][128] bf16, or fp32 */
+    OutPeers peers;             /* extra destinations of every output row */
     float *part_o;
     float2 *part_ml;
+    uint32_t *fix_counters;     /* [cut items][2 M tiles][4 row quarters] arrivals */
     uint32_t *status;
 };
 
@@ -192,6 +212,35 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity,
     }
     atomicExch(&misc->abort_flag, 1u);
     return false;
+}
+
+/* Store 32 consecutive columns of one output row (already normalised) to the
+ * local output and to every peer destination. */
+__device__ __forceinline__ void store_row_chunk(const AttnParams &p, size_t off,
+                                                const float *v) {
+    if (p.out_fp32) {
+#pragma unroll
+        for (uint32_t i = 0; i < 8; i++) {
+            const float4 f = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + off + i * 4) = f;
+            for (uint32_t d = 0; d < p.peers.n; d++)
+                *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.peers.ptr[d]) + off +
+                                            i * 4) = f;
+        }
+    } else {
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i++) {
+            uint4 u;
+            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&u);
+#pragma unroll
+            for (uint32_t e = 0; e < 4; e++)
+                h[e] = __floats2bfloat162_rn(v[i * 8 + 2 * e], v[i * 8 + 2 * e + 1]);
+            *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + off + i * 8) = u;
+            for (uint32_t d = 0; d < p.peers.n; d++)
+                *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.peers.ptr[d]) +
+                                           off + i * 8) = u;
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -551,39 +600,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
+            const size_t orow = ((size_t)token * p.n_heads + head) * Q3_D;
             if (seg.partial_slot < 0) {
                 const float inv = 1.0f / l;
-                const size_t orow = ((size_t)token * p.n_heads + head) * Q3_D;
-                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.out) + orow;
-                float *dst32 = reinterpret_cast<float *>(p.out) + orow;
 #pragma unroll
                 for (uint32_t ch = 0; ch < 4; ch++) {
                     uint32_t o[32];
                     tmem_ld32(o_addr + ch * 32u, o);
                     tmem_wait_ld();
-                    if (valid && p.out_fp32) {
+                    float v[32];
 #pragma unroll
-                        for (uint32_t i = 0; i < 8; i++)
-                            *reinterpret_cast<float4 *>(dst32 + ch * 32 + i * 4) = make_float4(
-                                __uint_as_float(o[i * 4]) * inv,
-                                __uint_as_float(o[i * 4 + 1]) * inv,
-                                __uint_as_float(o[i * 4 + 2]) * inv,
-                                __uint_as_float(o[i * 4 + 3]) * inv);
-                    } else if (valid) {
-#pragma unroll
-                        for (uint32_t i = 0; i < 4; i++) {
-                            uint4 u;
-                            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&u);
-#pragma unroll
-                            for (uint32_t e = 0; e < 4; e++)
-                                h[e] = __floats2bfloat162_rn(
-                                    __uint_as_float(o[i * 8 + 2 * e]) * inv,
-                                    __uint_as_float(o[i * 8 + 2 * e + 1]) * inv);
-                            *reinterpret_cast<uint4 *>(dst + ch * 32 + i * 8) = u;
-                        }
-                    }
+                    for (uint32_t i = 0; i < 32; i++) v[i] = __uint_as_float(o[i]) * inv;
+                    if (valid) store_row_chunk(p, orow + ch * 32, v);
                 }
             } else {
+                /* piece of a cut item: publish the un-normalised partial ... */
                 const size_t prow = (size_t)seg.partial_slot * 256 + q * 128 + row;
                 float *dst = p.part_o + prow * Q3_D;
 #pragma unroll
@@ -598,6 +629,80 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 }
                 p.part_ml[prow] =
                     make_float2(m_ref == -INFINITY ? -INFINITY : m_ref * c, l);
+                __threadfence();
+                /* ... and count the arrival of this warp's 32 rows. The warp
+                 * that arrives last at (item, M tile, row quarter) combines all
+                 * pieces of those rows; nobody waits for anybody:
+                 *   M = max_i m_i;  out = sum_i 2^(m_i-M) O_i / sum_i 2^(m_i-M) l_i
+                 * equal to one running max over all keys
+                 * (ref: src/q3_forward.cu:452-518) up to rounding. */
+                __syncwarp();
+                uint32_t last = 0;
+                if (lane == 0) {
+                    uint32_t *cnt = p.fix_counters + (seg.fix_index * 2 + q) * 4 + (warp & 3u);
+                    last = atomicAdd(cnt, 1u) + 1 == seg.slot_count;
+                    if (last) *cnt = 0;            /* ready for the next launch */
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    /* this thread's own partial is still in tensor memory; only
+                     * the other pieces' rows are read back (from L2) */
+                    const uint32_t own = (uint32_t)seg.partial_slot - seg.slot_begin;
+                    const size_t base = (size_t)seg.slot_begin * 256 + q * 128 + row;
+                    const float m_own = m_ref == -INFINITY ? -INFINITY : m_ref * c;
+                    float M = m_own;
+                    for (uint32_t i = 0; i < seg.slot_count; i++)
+                        if (i != own)
+                            M = fmaxf(M, __ldcg(&p.part_ml[base + (size_t)i * 256]).x);
+                    /* sums run in slot order whichever piece came last, so the
+                     * result is bit-identical from run to run */
+                    const float w_own = m_own == -INFINITY ? 0.f : exp2f(m_own - M);
+                    float den = 0.f;
+                    for (uint32_t i = 0; i < seg.slot_count; i++) {
+                        if (i == own) {
+                            den += w_own * l;
+                        } else {
+                            const float2 ml = __ldcg(&p.part_ml[base + (size_t)i * 256]);
+                            den += ml.x == -INFINITY ? 0.f : exp2f(ml.x - M) * ml.y;
+                        }
+                    }
+                    const float inv = 1.0f / den;
+#pragma unroll 1
+                    for (uint32_t ch = 0; ch < 4; ch++) {
+                        uint32_t o[32];
+                        tmem_ld32(o_addr + ch * 32u, o);
+                        tmem_wait_ld();
+                        float v[32];
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; i++) v[i] = 0.f;
+                        for (uint32_t sidx = 0; sidx < seg.slot_count; sidx++) {
+                            if (sidx == own) {
+                                const float wgt = w_own * inv;
+#pragma unroll
+                                for (uint32_t i = 0; i < 32; i++)
+                                    v[i] += wgt * __uint_as_float(o[i]);
+                                continue;
+                            }
+                            const size_t r2 = base + (size_t)sidx * 256;
+                            const float mx2 = __ldcg(&p.part_ml[r2]).x;
+                            const float wgt = mx2 == -INFINITY ? 0.f : exp2f(mx2 - M) * inv;
+                            const float4 *src = reinterpret_cast<const float4 *>(
+                                p.part_o + r2 * Q3_D + ch * 32);
+                            float4 f[8];
+#pragma unroll
+                            for (uint32_t i = 0; i < 8; i++) f[i] = __ldcg(src + i);
+#pragma unroll
+                            for (uint32_t i = 0; i < 8; i++) {
+                                v[i * 4] += wgt * f[i].x;
+                                v[i * 4 + 1] += wgt * f[i].y;
+                                v[i * 4 + 2] += wgt * f[i].z;
+                                v[i * 4 + 3] += wgt * f[i].w;
+                            }
+                        }
+                        if (valid) store_row_chunk(p, orow + ch * 32, v);
+                    }
+                }
             }
             /* the next segment's first PV overwrites O_q only after p_full of
              * its first tile, which this thread raises after these loads */
@@ -611,57 +716,59 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-/* Combine the partials of items that were cut across CTAs:
- *   M = max_i m_i;  out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i
- * which equals the single-pass result (ref: one running max over both
- * segments, src/q3_forward.cu:452-518) up to rounding. One warp per row. */
-__global__ void __launch_bounds__(256)
-merge_partials_kernel(const q3_merge_item *__restrict__ merges,
-                      const float *__restrict__ part_o,
-                      const float2 *__restrict__ part_ml, uint32_t tokens,
-                      uint32_t n_heads, uint32_t out_fp32, void *__restrict__ out) {
-    const q3_merge_item mi = merges[blockIdx.x];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    for (uint32_t r = blockIdx.y * 8 + warp; r < 256; r += gridDim.y * 8) {
-        const uint32_t token = mi.tok0 + (r >> 7) * 16u + ((r & 127u) >> 3);
-        if (token >= tokens) continue;
-        const uint32_t head = mi.kv_head * Q3_G + (r & 7u);
-        float M = -INFINITY;
-        for (uint32_t i = 0; i < mi.slot_count; i++)
-            M = fmaxf(M, part_ml[(size_t)(mi.slot_begin + i) * 256 + r].x);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float den = 0.f;
-        for (uint32_t i = 0; i < mi.slot_count; i++) {
-            const size_t prow = (size_t)(mi.slot_begin + i) * 256 + r;
-            const float2 ml = part_ml[prow];
-            const float w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);
-            den += w * ml.y;
-            const float4 o = *reinterpret_cast<const float4 *>(part_o + prow * Q3_D + lane * 4);
-            acc.x += w * o.x;
-            acc.y += w * o.y;
-            acc.z += w * o.z;
-            acc.w += w * o.w;
-        }
-        const float inv = 1.0f / den;
-        const size_t off = ((size_t)token * n_heads + head) * Q3_D + lane * 4;
-        if (out_fp32) {
-            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + off) =
-                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-        } else {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-            uint2 u;
-            u.x = *reinterpret_cast<uint32_t *>(&lo);
-            u.y = *reinterpret_cast<uint32_t *>(&hi);
-            *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(out) + off) = u;
-        }
+/* After a layer's rows are stored: publish `seq` in every rank's flag array
+ * (slot = this rank). One thread; the fence orders the flag after the rows of
+ * the preceding kernels of this stream. */
+__global__ void gather_signal_kernel(const GatherFlags flags, uint32_t rank, uint32_t seq) {
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (uint32_t d = 0; d < flags.n; d++)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.ptr[d] + rank),
+                         "r"(seq)
+                         : "memory");
     }
+}
+
+/* Wait (bounded) until every rank has published at least `seq` in this rank's
+ * flag array, i.e. the gathered buffer holds that layer from every rank. */
+__global__ void gather_wait_kernel(const uint32_t *flags, uint32_t n_ranks, uint32_t seq,
+                                   uint32_t *status) {
+    const uint32_t r = threadIdx.x;
+    if (r >= n_ranks) return;
+    for (uint32_t i = 0; i < (1u << 24); i++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+        if ((int32_t)(v - seq) >= 0) return;
+        __nanosleep(64);
+    }
+    atomicOr(status, Q3_STATUS_GATHER_TIMEOUT);
 }
 
 }  // namespace
 
+bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
+                             char *error, size_t error_len) {
+    GatherFlags f;
+    f.n = g->n_ranks;
+    for (uint32_t d = 0; d < g->n_ranks; d++) f.ptr[d] = g->flags[d];
+    gather_signal_kernel<<<1, 32, 0, rt->stream>>>(f, g->rank, seq);
+    Q3_LAUNCH_CHECK("gather_signal launch failed");
+    rt->n_launch++;
+    return true;
+}
+
+bool q3_launch_gather_wait(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
+                           char *error, size_t error_len) {
+    gather_wait_kernel<<<1, 32, 0, rt->stream>>>(g->flags[g->rank], g->n_ranks, seq,
+                                                 rt->status_dev);
+    Q3_LAUNCH_CHECK("gather_wait launch failed");
+    rt->n_launch++;
+    return true;
+}
+
 bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st,
-                         void *out_bf16, char *error, size_t error_len) {
+                         void *out_bf16, const q3_gather_peers *gather, char *error,
+                         size_t error_len) {
     const q3_attn_config &c = rt->cfg;
     static bool attr_set = false;
     if (!attr_set) {
@@ -692,8 +799,19 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st
     p.scale_log2 = (1.0f / sqrtf((float)Q3_D)) * 1.4426950408889634f;
     p.out_fp32 = c.out_fp32;
     p.out = out_bf16;
+    p.peers.n = 0;
+    if (gather) {
+        /* rows of this rank go to slot `rank` of every OTHER rank's gathered
+         * buffer; the local slot is `out_bf16` itself */
+        const size_t slot_bytes = (size_t)st->tokens * c.n_heads * Q3_D * (c.out_fp32 ? 4 : 2);
+        for (uint32_t d = 0; d < gather->n_ranks; d++)
+            if (d != gather->rank)
+                p.peers.ptr[p.peers.n++] =
+                    (uint8_t *)gather->gathered[d] + slot_bytes * gather->rank;
+    }
     p.part_o = rt->part_o;
     p.part_ml = rt->part_ml;
+    p.fix_counters = rt->fix_counters;
     p.status = rt->status_dev;
     q3_phase_begin(rt, Q3_PHASE_ATTENTION);
     attention_tc_kernel<<<st->grid, kThreads, kSmemTotal, rt->stream>>>(q_map, rt->k_map,
@@ -701,15 +819,5 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st
     q3_phase_end(rt);
     Q3_LAUNCH_CHECK("attention_tc launch failed");
     rt->n_launch++;
-    if (st->n_merges) {
-        dim3 grid(st->n_merges, 8);
-        q3_phase_begin(rt, Q3_PHASE_MERGE);
-        merge_partials_kernel<<<grid, 256, 0, rt->stream>>>(
-            st->merges, rt->part_o, rt->part_ml, st->tokens, c.n_heads, c.out_fp32,
-            out_bf16);
-        q3_phase_end(rt);
-        Q3_LAUNCH_CHECK("merge_partials launch failed");
-        rt->n_launch++;
-    }
     return true;
 }

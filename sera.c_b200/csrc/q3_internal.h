@@ -23,6 +23,7 @@
 
 /* device_status bits (set by kernels whose bounded waits gave up) */
 #define Q3_STATUS_WAIT_TIMEOUT 1u
+#define Q3_STATUS_GATHER_TIMEOUT 2u
 
 static inline void q3_clear_error(char *error, size_t error_len) {
     if (error && error_len) error[0] = '\0';
@@ -73,6 +74,7 @@ struct q3_attn_runtime {
     float *part_o;     /* [slots][256][128] */
     float2 *part_ml;   /* [slots][256] (max in log2 units, sum) */
     uint32_t part_slots;
+    uint32_t *fix_counters; /* [part_slots][8] arrival counters, zero between launches */
 
     /* decode split partials */
     float *dec_o;      /* [dec_slots][8][128] */
@@ -202,8 +204,13 @@ bool q3_launch_kvwrite(q3_attn_runtime *rt, uint32_t layer, const void *q,
                        const uint32_t *dst_slot, void *q_out, char *error,
                        size_t error_len);
 bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer,
-                         const q3_stage *st, void *out_bf16, char *error,
+                         const q3_stage *st, void *out_bf16,
+                         const q3_gather_peers *gather, char *error,
                          size_t error_len);
+bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
+                             char *error, size_t error_len);
+bool q3_launch_gather_wait(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
+                           char *error, size_t error_len);
 bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer,
                       const q3_decode_plan *plan, bool with_new_token,
                       void *out_bf16, char *error, size_t error_len);

@@ -158,6 +158,7 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     rt->q2 = nullptr;
     rt->part_o = nullptr;
     rt->part_ml = nullptr;
+    rt->fix_counters = nullptr;
     rt->dec_o = nullptr;
     rt->dec_ml = nullptr;
     rt->dec_slots = 0;
@@ -186,6 +187,8 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     ok = ok && rt_malloc(rt, (void **)&rt->q2, q2_bytes) == cudaSuccess;
     ok = ok && rt_malloc(rt, (void **)&rt->part_o, part_o_bytes) == cudaSuccess;
     ok = ok && rt_malloc(rt, (void **)&rt->part_ml, part_ml_bytes) == cudaSuccess;
+    ok = ok && rt_malloc(rt, (void **)&rt->fix_counters,
+                         (size_t)rt->part_slots * 8 * sizeof(uint32_t)) == cudaSuccess;
     ok = ok && rt_malloc(rt, (void **)&rt->qk_norm_w, w_bytes) == cudaSuccess;
     ok = ok && rt_malloc(rt, (void **)&rt->rope_table, rope_bytes) == cudaSuccess;
     ok = ok && rt_malloc(rt, (void **)&rt->status_dev, sizeof(uint32_t)) == cudaSuccess;
@@ -204,6 +207,8 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     cudaMemsetAsync(rt->v_pool, 0, pool_bytes, rt->stream);
     cudaMemsetAsync(rt->q2, 0, q2_bytes, rt->stream);
     cudaMemsetAsync(rt->status_dev, 0, sizeof(uint32_t), rt->stream);
+    cudaMemsetAsync(rt->fix_counters, 0, (size_t)rt->part_slots * 8 * sizeof(uint32_t),
+                    rt->stream);
 
     /* QK-norm weights default to 1 (ref: synthetic configs use weight 1). */
     {
@@ -257,6 +262,7 @@ extern "C" void q3_attn_destroy(q3_attn_runtime *rt) {
     rt_free(rt, rt->q2);
     rt_free(rt, rt->part_o);
     rt_free(rt, rt->part_ml);
+    rt_free(rt, rt->fix_counters);
     rt_free(rt, rt->dec_o);
     rt_free(rt, rt->dec_ml);
     rt_free(rt, rt->qk_norm_w);
@@ -623,7 +629,7 @@ extern "C" bool q3_prefix_prefill_layer(q3_prefix_kv *prefix, uint32_t layer,
     if (!q3_launch_kvwrite(rt, layer, q, k, v, tokens, st->rope_pos, st->dst_page,
                            st->dst_slot, rt->q2, error, error_len))
         return false;
-    return q3_launch_attention(rt, layer, st, out, error, error_len);
+    return q3_launch_attention(rt, layer, st, out, NULL, error, error_len);
 }
 
 extern "C" bool q3_prefix_advance(q3_prefix_kv *prefix, uint32_t tokens,
@@ -960,7 +966,46 @@ extern "C" bool q3_suffix_attention_layer(q3_pack_plan *plan, uint32_t layer,
     if (!q3_launch_kvwrite(rt, layer, q, k, v, plan->tokens, st->rope_pos, st->dst_page,
                            st->dst_slot, rt->q2, error, error_len))
         return false;
-    return q3_launch_attention(rt, layer, st, out, error, error_len);
+    return q3_launch_attention(rt, layer, st, out, NULL, error, error_len);
+}
+
+extern "C" bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t layer,
+                                                   const void *q, const void *k,
+                                                   const void *v,
+                                                   const q3_gather_peers *gather,
+                                                   uint32_t seq, char *error,
+                                                   size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!plan || !q || !k || !v || !gather || gather->n_ranks == 0 ||
+        gather->n_ranks > Q3_MAX_GATHER_RANKS || gather->rank >= gather->n_ranks)
+        return q3_fail(error, error_len,
+                       "q3_suffix_attention_layer_gathered: invalid argument");
+    for (uint32_t d = 0; d < gather->n_ranks; d++)
+        if (!gather->gathered[d] || !gather->flags[d])
+            return q3_fail(error, error_len,
+                           "q3_suffix_attention_layer_gathered: invalid argument");
+    q3_attn_runtime *rt = plan->prefix->rt;
+    if (layer >= rt->cfg.num_layers)
+        return q3_fail(error, error_len,
+                       "q3_suffix_attention_layer_gathered: layer out of range");
+    const q3_stage *st = plan->stage;
+    const size_t slot_bytes =
+        (size_t)plan->tokens * rt->cfg.n_heads * Q3_D * (rt->cfg.out_fp32 ? 4 : 2);
+    void *local = (uint8_t *)gather->gathered[gather->rank] + slot_bytes * gather->rank;
+    if (!q3_launch_kvwrite(rt, layer, q, k, v, plan->tokens, st->rope_pos, st->dst_page,
+                           st->dst_slot, rt->q2, error, error_len))
+        return false;
+    if (!q3_launch_attention(rt, layer, st, local, gather, error, error_len)) return false;
+    return q3_launch_gather_signal(rt, gather, seq, error, error_len);
+}
+
+extern "C" bool q3_attn_wait_gathered(q3_attn_runtime *rt, const q3_gather_peers *gather,
+                                      uint32_t seq, char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt || !gather || gather->n_ranks == 0 || gather->n_ranks > Q3_MAX_GATHER_RANKS ||
+        gather->rank >= gather->n_ranks || !gather->flags[gather->rank])
+        return q3_fail(error, error_len, "q3_attn_wait_gathered: invalid argument");
+    return q3_launch_gather_wait(rt, gather, seq, error, error_len);
 }
 
 extern "C" bool q3_cuda_qknorm_rope_kvwrite(q3_attn_runtime *rt, uint32_t layer,

@@ -171,8 +171,17 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
             s.merges.push_back(m);
         }
     }
-    std::vector<uint32_t> item_next(items.size(), 0);
+    std::vector<uint32_t> item_next(items.size(), 0), item_fix(items.size(), 0);
+    {
+        uint32_t n_fix = 0;
+        for (size_t i = 0; i < items.size(); i++)
+            if (item_pieces[i] > 1) item_fix[i] = n_fix++;
+    }
     for (uint32_t c = 0; c < grid; c++) {
+        /* pieces of cut items first: their last-arriver combination then
+         * happens early instead of at the very end of the launch */
+        std::stable_partition(per_cta[c].begin(), per_cta[c].end(),
+                              [&](const Piece &pc) { return item_pieces[pc.item] > 1; });
         s.cta_seg_begin[c] = (uint32_t)s.segments.size();
         for (const Piece &pc : per_cta[c]) {
             const Item &it = items[pc.item];
@@ -187,6 +196,10 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
                                    : -1;
             seg.run_begin = s.tile_run_begin[it.tt];
             seg.run_end = s.tile_run_begin[it.tt + 1];
+            seg.slot_begin = item_slot[pc.item];
+            seg.slot_count = item_pieces[pc.item] > 1 ? item_pieces[pc.item] : 0;
+            seg.fix_index = item_fix[pc.item];
+            seg.pad = 0;
             s.segments.push_back(seg);
         }
     }

@@ -12,9 +12,11 @@
  *               one key tile.
  *   segment     a contiguous range of key tiles of one item given to one CTA.
  *               The whole launch is cut stream-K style: every CTA receives the
- *               same number of key tiles (+-1); an item that is cut writes
- *               un-normalised partials that a merge pass combines with
- *               log-sum-exp.
+ *               same cost; every piece of a cut item writes un-normalised
+ *               partials, and the piece that finishes last combines them
+ *               with log-sum-exp inside the kernel (no waiting: an arrival
+ *               counter per item). A CTA runs its pieces of cut items before
+ *               its whole items, so those combinations happen early.
  */
 #ifndef Q3_SCHED_H
 #define Q3_SCHED_H
@@ -42,6 +44,10 @@ struct q3_segment {
     int32_t partial_slot;  /* -1: this segment is the whole item              */
     uint32_t run_begin;    /* runs[run_begin, run_end) of the token tile      */
     uint32_t run_end;
+    uint32_t slot_begin;   /* cut item: its partial slots [slot_begin, +count) */
+    uint32_t slot_count;
+    uint32_t fix_index;    /* cut item: index of its arrival counters          */
+    uint32_t pad;
 };
 
 struct q3_merge_item {

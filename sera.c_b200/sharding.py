@@ -41,3 +41,51 @@ def gathered_to_full(gathered):
     rank-major layout, such as a column-sharded o_proj, does not need it)."""
     n, T, h, D = gathered.shape
     return gathered.permute(1, 0, 2, 3).reshape(T, n * h, D)
+
+
+class PeerGather:
+    """Gathered output buffers in symmetric memory, for the attention kernels
+    that store their rows straight into every rank's buffer.
+
+    Each rank owns `depth` buffers [n, T, H/n, D] and one flag array per
+    buffer; `peers(i)` returns the descriptor (peer-mapped base pointers of all
+    ranks) the C ABI takes. No kernel of this repository loads from a peer:
+    ranks only store to peers and read their own memory.
+    """
+
+    def __init__(self, tokens, n_heads_local, head_dim, dtype, device, group=None, depth=2):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import GatherPeers
+        group = group or dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one box)")
+        self.shape = (self.world, tokens, n_heads_local, head_dim)
+        self.depth = depth
+        self.bufs, self.flags, self._desc, self._handles = [], [], [], []
+        for _ in range(depth):
+            buf = symm_mem.empty(self.shape, dtype=dtype, device=device)
+            flg = symm_mem.empty((64,), dtype=torch.int32, device=device)
+            buf.zero_()
+            flg.zero_()
+            hb = symm_mem.rendezvous(buf, group)
+            hf = symm_mem.rendezvous(flg, group)
+            d = GatherPeers()
+            d.n_ranks, d.rank = self.world, self.rank
+            for r in range(self.world):
+                d.gathered[r] = hb.buffer_ptrs[r]
+                d.flags[r] = hf.buffer_ptrs[r]
+            self.bufs.append(buf)
+            self.flags.append(flg)
+            self._desc.append(d)
+            self._handles += [hb, hf]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def peers(self, i):
+        return self._desc[i % self.depth]
+
+    def full(self, i):
+        """[T, H, D] view-copy of buffer i (after the wait for its layer)."""
+        return gathered_to_full(self.bufs[i % self.depth])

@@ -41,12 +41,12 @@ def max_err_vs_bf16_oracle(got, ref):
     return float(e.max() / np.abs(ref).max())
 
 
-def dev(a, dtype):
-    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(dtype).contiguous()
+def dev(a, dtype, device="cuda"):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device).to(dtype).contiguous()
 
 
 def run_case_native(pkg, case, out_fp32=False, prefill_chunks=None, permute_pages=True,
-                    layer=1, seed=0, return_runtime=False):
+                    layer=1, seed=0, return_runtime=False, device=0):
     """Prefix prefill (optionally in chunks) + packed suffix pass through the C
     ABI. Inputs are given as bf16. Returns the attention output [T,H,D] fp32."""
     P, S, T = case.P, case.S, case.T
@@ -59,11 +59,12 @@ def run_case_native(pkg, case, out_fp32=False, prefill_chunks=None, permute_page
     rt = pkg.Runtime(num_layers=2, n_heads=case.H, n_kv_heads=case.Hkv,
                      max_positions=P + max_suffix + 8, max_tokens=max(P, S, 1),
                      num_pages=num_pages, out_fp32=out_fp32, rms_eps=case.eps,
-                     rope_theta=case.theta)
+                     rope_theta=case.theta, device=device)
+    cuda = torch.device("cuda", device)
     rt.set_qk_norm(layer, case.q_norm_w, case.k_norm_w)
     odt = torch.float32 if out_fp32 else torch.bfloat16
-    out = torch.zeros(T, case.H, case.D, dtype=odt, device="cuda")
-    q, k, v = (dev(a, torch.bfloat16) for a in (case.q, case.k, case.v))
+    out = torch.zeros(T, case.H, case.D, dtype=odt, device=cuda)
+    q, k, v = (dev(a, torch.bfloat16, cuda) for a in (case.q, case.k, case.v))
     if permute_pages:
         perm = rng.permutation(num_pages).astype(np.uint32)
         taken = rt.alloc_pages(num_pages)   # empty the free list; we hand out ids
