@@ -282,17 +282,18 @@ bool q3_suffix_attention_layer(q3_pack_plan *plan, uint32_t layer,
                                const void *q, const void *k, const void *v,
                                void *out, char *error, size_t error_len);
 
-/* --- head-sharded runs: attention fused with the output all-gather ------ *
+/* --- head-sharded runs: attention + output all-gather ------------------- *
  * New (the reference is single-device). With the KV heads sharded over the
- * GPUs of one box, every rank needs all heads' outputs after a layer. Instead
- * of a separate collective, the attention and merge kernels store each output
- * row into the gathered buffer of every rank: `gathered[r]` is the base of rank
- * r's buffer [n_ranks][tokens][n_heads][128] (bf16, or fp32 with out_fp32),
- * mapped into this process (peer memory over NVLink); this rank fills slot
- * `rank` of each. `flags[r]` is rank r's array of n_ranks uint32 (also peer
- * mapped, zero-initialised): after the layer's stores, `seq` is published in
- * flags[r][rank] for every r. q3_attn_wait_gathered queues a bounded
- * device-side wait until this rank's flags all reached `seq`, i.e. its
+ * GPUs of one box, every rank needs all heads' outputs after a layer.
+ * `gathered[r]` is the base of rank r's buffer [n_ranks][tokens][n_heads][128]
+ * (bf16, or fp32 with out_fp32), mapped into this process (peer memory over
+ * NVLink). The call writes this rank's rows into slot `rank` of its own buffer
+ * and queues, on a side stream, copy-engine copies of that slot into slot
+ * `rank` of every other rank's buffer (no SM is used, so the next layer's
+ * kernels keep the whole GPU), followed by the flags: `flags[r]` is rank r's
+ * array of n_ranks uint32 (peer mapped, zero-initialised) and `seq` is
+ * published in flags[r][rank] for every r. q3_attn_wait_gathered queues a
+ * bounded device-side wait until this rank's flags all reached `seq`, i.e. its
  * gathered buffer holds that layer from every rank (timeout: status bit 2,
  * reported by q3_attn_synchronize). seq must increase; comparisons wrap. */
 #define Q3_MAX_GATHER_RANKS 8u

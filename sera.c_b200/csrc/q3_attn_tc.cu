@@ -747,11 +747,11 @@ __global__ void gather_wait_kernel(const uint32_t *flags, uint32_t n_ranks, uint
 }  // namespace
 
 bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
-                             char *error, size_t error_len) {
+                             cudaStream_t stream, char *error, size_t error_len) {
     GatherFlags f;
     f.n = g->n_ranks;
     for (uint32_t d = 0; d < g->n_ranks; d++) f.ptr[d] = g->flags[d];
-    gather_signal_kernel<<<1, 32, 0, rt->stream>>>(f, g->rank, seq);
+    gather_signal_kernel<<<1, 32, 0, stream>>>(f, g->rank, seq);
     Q3_LAUNCH_CHECK("gather_signal launch failed");
     rt->n_launch++;
     return true;

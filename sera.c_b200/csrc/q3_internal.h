@@ -94,6 +94,11 @@ struct q3_attn_runtime {
     cudaEvent_t ev_in[3], ev_compute[3], ev_out[3];
     bool copy_ready;
     uint64_t host_calls;
+    /* head-sharded runs: copies of this rank's rows to the other ranks */
+    cudaStream_t gather_stream;
+    cudaEvent_t ev_gather[4];
+    bool gather_ready;
+    uint64_t gather_calls;
 
     uint64_t n_alloc, n_free, n_sync, n_launch;
     uint64_t workspace_bytes;
@@ -208,7 +213,7 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer,
                          const q3_gather_peers *gather, char *error,
                          size_t error_len);
 bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
-                             char *error, size_t error_len);
+                             cudaStream_t stream, char *error, size_t error_len);
 bool q3_launch_gather_wait(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
                            char *error, size_t error_len);
 bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer,

@@ -169,6 +169,9 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     rt->h2d_stream = rt->d2h_stream = nullptr;
     rt->copy_ready = false;
     rt->host_calls = 0;
+    rt->gather_stream = nullptr;
+    rt->gather_ready = false;
+    rt->gather_calls = 0;
     rt->n_alloc = rt->n_free = rt->n_sync = rt->n_launch = 0;
     rt->workspace_bytes = 0;
     rt->timing_on = false;
@@ -270,6 +273,11 @@ extern "C" void q3_attn_destroy(q3_attn_runtime *rt) {
     rt_free(rt, rt->status_dev);
     rt_free(rt, rt->dev_stage);
     for (cudaEvent_t e : rt->ev) cudaEventDestroy(e);
+    if (rt->gather_ready) {
+        cudaStreamSynchronize(rt->gather_stream);
+        for (int i = 0; i < 4; i++) cudaEventDestroy(rt->ev_gather[i]);
+        cudaStreamDestroy(rt->gather_stream);
+    }
     if (rt->copy_ready) {
         cudaStreamSynchronize(rt->h2d_stream);
         cudaStreamSynchronize(rt->d2h_stream);
@@ -318,6 +326,7 @@ extern "C" bool q3_attn_synchronize(q3_attn_runtime *rt, char *error,
                     cudaMemcpyDeviceToHost, rt->stream);
     cudaError_t e = cudaStreamSynchronize(rt->stream);
     if (e == cudaSuccess && rt->copy_ready) e = cudaStreamSynchronize(rt->d2h_stream);
+    if (e == cudaSuccess && rt->gather_ready) e = cudaStreamSynchronize(rt->gather_stream);
     rt->n_sync++;
     if (e != cudaSuccess)
         return q3_fail_cuda(error, error_len, "q3_attn_synchronize", e);
@@ -995,8 +1004,36 @@ extern "C" bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t 
     if (!q3_launch_kvwrite(rt, layer, q, k, v, plan->tokens, st->rope_pos, st->dst_page,
                            st->dst_slot, rt->q2, error, error_len))
         return false;
-    if (!q3_launch_attention(rt, layer, st, local, gather, error, error_len)) return false;
-    return q3_launch_gather_signal(rt, gather, seq, error, error_len);
+    /* The kernels write this rank's slot of its own gathered buffer. The copies
+     * to the other ranks go through the copy engines on a side stream (NVLink,
+     * no SM involved), overlapped with the next layer's kernels; the flags are
+     * published after them on the same stream. (The kernels can also store the
+     * rows into peer memory themselves - q3_launch_attention takes the peer
+     * list - but scattered 16-byte remote stores from the softmax warps
+     * stalled them: 450 us instead of 250 us per layer at 8 GPUs.) */
+    if (!q3_launch_attention(rt, layer, st, local, NULL, error, error_len)) return false;
+    if (!rt->gather_ready) {
+        bool ok = cudaStreamCreateWithFlags(&rt->gather_stream, cudaStreamNonBlocking) ==
+                  cudaSuccess;
+        for (int i = 0; i < 4 && ok; i++)
+            ok = cudaEventCreateWithFlags(&rt->ev_gather[i], cudaEventDisableTiming) ==
+                 cudaSuccess;
+        if (!ok)
+            return q3_fail(error, error_len,
+                           "q3_suffix_attention_layer_gathered: stream set-up failed");
+        rt->gather_ready = true;
+    }
+    cudaEvent_t ev = rt->ev_gather[rt->gather_calls++ % 4];
+    cudaError_t e = cudaEventRecord(ev, rt->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(rt->gather_stream, ev, 0);
+    for (uint32_t d = 0; d < gather->n_ranks && e == cudaSuccess; d++)
+        if (d != gather->rank)
+            e = cudaMemcpyAsync((uint8_t *)gather->gathered[d] + slot_bytes * gather->rank,
+                                local, slot_bytes, cudaMemcpyDeviceToDevice,
+                                rt->gather_stream);
+    if (e != cudaSuccess)
+        return q3_fail_cuda(error, error_len, "q3_suffix_attention_layer_gathered: copy", e);
+    return q3_launch_gather_signal(rt, gather, seq, rt->gather_stream, error, error_len);
 }
 
 extern "C" bool q3_attn_wait_gathered(q3_attn_runtime *rt, const q3_gather_peers *gather,
