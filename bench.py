@@ -49,6 +49,10 @@ UNIT = "tokens/s"
 PAIRS_PER_HEAD = TOKENS * PREFIX + BRANCHES * (SUFFIX * (SUFFIX + 1) // 2)
 FLOPS_PER_LAYER = 4 * D * H * PAIRS_PER_HEAD
 FLOPS_PER_STEP = FLOPS_PER_LAYER * L
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at N = 1, from the
+# ncu capture summarised in profiles/attention_tc_kernel__stack_layer_p32768_b128x16.md
+# (205.8 MB read + 49.9 MB written; algorithmic bytes 218 MB). Scales with 1/N.
+ATTENTION_DRAM_BYTES_PER_LAUNCH = 255.6e6
 
 
 def measured_peaks():
@@ -291,7 +295,9 @@ def run_ours(args):
             "clocks": clocks,
             "roofline": {"kernel": "attention_tc_kernel", "bound": "tensor",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak,
+                         "traffic": ATTENTION_DRAM_BYTES_PER_LAUNCH / n_gpus,
+                         "traffic_unit": "bytes per launch (ncu capture, see profiles/)",
                          "peak_source": "%s bf16 sustained" % peaks["source"],
                          "ms_per_launch": per_launch_ms, "launches": attn_n,
                          "flops_per_launch": flops_per_launch},
