@@ -345,19 +345,20 @@ decode_merge_kernel(const uint32_t *__restrict__ seq_work_begin, uint32_t num_se
 
 }  // namespace
 
+/* Per device, at runtime creation: opt in to the large dynamic shared memory. */
+bool q3_prepare_decode_kernel(char *error, size_t error_len) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kDecSmemTotal);
+    if (e != cudaSuccess)
+        return q3_fail_cuda(error, error_len, "decode: shared memory opt-in", e);
+    return true;
+}
+
 bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer, const q3_decode_plan *plan,
                       bool with_new_token, void *out_bf16, char *error,
                       size_t error_len) {
     const q3_attn_config &c = rt->cfg;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kDecSmemTotal);
-        if (e != cudaSuccess)
-            return q3_fail_cuda(error, error_len, "decode: shared memory opt-in", e);
-        attr_set = true;
-    }
     DecodeParams p;
     p.work = plan->work;
     p.seq_work_begin = plan->seq_work_begin;

@@ -88,7 +88,7 @@ struct Barriers {
     uint64_t q_full, q_empty;
     uint64_t k_full[kStages], k_empty[kStages];
     uint64_t v_full[kStages], v_empty[kStages];
-    uint64_t s_full[kNQ], p_full[kNQ], o_full[kNQ];
+    uint64_t s_full[kNQ], p_half[kNQ][2], o_full[kNQ];
 };
 
 struct Misc {
@@ -187,9 +187,13 @@ __device__ __forceinline__ void exp2_poly2(uint64_t x2, float &p0, float &p1) {
     p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(xr0) << 23));
     p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(xr1) << 23));
 }
-/* pairs out of every 8 whose exponentials go through exp2_poly2 */
+/* Pairs out of every 8 whose exponentials go through exp2_poly2. Measured on
+ * B200 (one layer of the benchmark stack, TFLOP/s): 0 -> 1195, 1 -> 1177,
+ * 2 -> 1170, 3 -> 1136: the loop is latency- and power-bound rather than
+ * MUFU-throughput-bound, so the extra FMA-pipe instructions do not pay; the
+ * path is kept for parts with a different balance. */
 #ifndef Q3_POLY_PAIRS_OF_8
-#define Q3_POLY_PAIRS_OF_8 1
+#define Q3_POLY_PAIRS_OF_8 0
 #endif
 
 /* Register budget: setmaxnreg must be executed identically by all four warps
@@ -265,7 +269,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         for (uint32_t q = 0; q < kNQ; q++) {
             mbar_init(&bar.s_full[q], 1);
-            mbar_init(&bar.p_full[q], 128);
+            mbar_init(&bar.p_half[q][0], 128);
+            mbar_init(&bar.p_half[q][1], 128);
             mbar_init(&bar.o_full[q], 1);
         }
         misc->abort_flag = 0;
@@ -415,16 +420,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 }
                 umma_commit(&bar.s_full[q]);
             };
-            auto issue_pv = [&](uint32_t q, uint32_t stage, bool accumulate) {
-                /* O_q += P_q V : 8 steps of K = 16 keys; V is MN-major
-                 * (64-column blocks 16 KiB apart, 8-key groups 1 KiB apart) */
+            auto issue_pv = [&](uint32_t q, uint32_t stage, bool accumulate, uint32_t half) {
+                /* O_q += P_q V for keys [64*half, 64*half+64): 4 steps of K = 16
+                 * keys; V is MN-major (64-column blocks 16 KiB apart, 8-key groups
+                 * 1 KiB apart). P arrives in two halves so that the first half's
+                 * MMAs overlap the second half's exponentials. */
 #pragma unroll
-                for (uint32_t ks = 0; ks < 8; ks++)
+                for (uint32_t ks = half * 4; ks < half * 4 + 4; ks++)
                     umma_ts(tmem + kColO + q * 128u, tmem + kColS + q * 128u + ks * 8u,
                             umma_desc(v_addr + stage * kTileBytes + ks * 2048u, kHalfBytes,
                                       1024),
                             idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
-                umma_commit(&bar.o_full[q]);
+                if (half == 1) umma_commit(&bar.o_full[q]);
             };
 
             for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
@@ -450,12 +457,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     const uint32_t nph = ((it + 1) / kStages) & 1u;
                     const bool more = j + 1 < n;
                     for (uint32_t q = 0; q < kNQ && alive; q++) {
-                        alive = wait_or_abort(&bar.p_full[q], it & 1u, misc);
+                        alive = wait_or_abort(&bar.p_half[q][0], it & 1u, misc);
                         if (alive && q == 0)
                             alive = wait_or_abort(&bar.v_full[stage], ph, misc);
                         if (!alive) break;
                         tc_fence_after();
-                        issue_pv(q, stage, j > 0);
+                        issue_pv(q, stage, j > 0, 0);
+                        alive = wait_or_abort(&bar.p_half[q][1], it & 1u, misc);
+                        if (!alive) break;
+                        tc_fence_after();
+                        issue_pv(q, stage, j > 0, 1);
                         if (q == kNQ - 1) umma_commit(&bar.v_empty[stage]);
                         if (more) {
                             if (q == 0) {
@@ -571,6 +582,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                     for (uint32_t i = 0; i < 64; i++) {
+                        if (i == 32) {
+                            /* keys 0..63 are ready: let their PV steps start */
+                            tmem_st32(s_addr, pk);
+                            tmem_wait_st();
+                            tc_fence_before();
+                            mbar_arrive(&bar.p_half[q][0]);
+                        }
                         float x0, x1, p0, p1;
                         const uint64_t x2 = ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, neg2);
                         unpack2(x2, x0, x1);
@@ -588,11 +606,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     unpack2(fadd2(fadd2(acc[0], acc[1]), fadd2(acc[2], acc[3])), a0, a1);
                     l += a0 + a1;
                 }
-                tmem_st32(s_addr, pk);
                 tmem_st32(s_addr + 32u, pk + 32);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bar.p_full[q]);
+                mbar_arrive(&bar.p_half[q][1]);
             }
             if (!alive) break;
             /* ---- segment epilogue: O_q of the last tile ---- */
@@ -766,19 +783,20 @@ bool q3_launch_gather_wait(q3_attn_runtime *rt, const q3_gather_peers *g, uint32
     return true;
 }
 
+/* Per device, at runtime creation: opt in to the large dynamic shared memory. */
+bool q3_prepare_attention_kernel(char *error, size_t error_len) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kSmemTotal);
+    if (e != cudaSuccess)
+        return q3_fail_cuda(error, error_len, "attention_tc: shared memory opt-in", e);
+    return true;
+}
+
 bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st,
                          void *out_bf16, const q3_gather_peers *gather, char *error,
                          size_t error_len) {
     const q3_attn_config &c = rt->cfg;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kSmemTotal);
-        if (e != cudaSuccess)
-            return q3_fail_cuda(error, error_len, "attention_tc: shared memory opt-in", e);
-        attr_set = true;
-    }
     CUtensorMap q_map;
     if (!q3_encode_tmap_q(&q_map, rt->q2, c.n_heads, st->tokens, error, error_len))
         return false;

@@ -220,6 +220,17 @@ bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer,
                       const q3_decode_plan *plan, bool with_new_token,
                       void *out_bf16, char *error, size_t error_len);
 
+bool q3_prepare_attention_kernel(char *error, size_t error_len);
+bool q3_prepare_decode_kernel(char *error, size_t error_len);
+
+/* Entry points make the runtime's device current: a host that drives several
+ * GPUs from one thread would otherwise launch on whichever device it left. */
+static inline bool q3_use_device(const q3_attn_runtime *rt, char *error, size_t error_len) {
+    cudaError_t e = cudaSetDevice(rt->cfg.device);
+    if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "cudaSetDevice", e);
+    return true;
+}
+
 bool q3_encode_tmap_2d(CUtensorMap *map, const void *base, uint64_t inner,
                        uint64_t rows, uint32_t box_inner, uint32_t box_rows,
                        char *error, size_t error_len);

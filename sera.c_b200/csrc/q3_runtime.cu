@@ -247,6 +247,11 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
         q3_attn_destroy(rt);
         return NULL;
     }
+    if (!q3_prepare_attention_kernel(error, error_len) ||
+        !q3_prepare_decode_kernel(error, error_len)) {
+        q3_attn_destroy(rt);
+        return NULL;
+    }
     rt->free_pages.resize(c.num_pages);
     for (uint32_t i = 0; i < c.num_pages; i++) rt->free_pages[i] = c.num_pages - 1 - i;
     if (cudaGetLastError() != cudaSuccess) {
@@ -602,6 +607,7 @@ extern "C" bool q3_prefix_prefill_layer(q3_prefix_kv *prefix, uint32_t layer,
     if (!prefix || !q || !k || !v || !out || tokens == 0)
         return q3_fail(error, error_len, "q3_prefix_prefill_layer: invalid argument");
     q3_attn_runtime *rt = prefix->rt;
+    if (!q3_use_device(rt, error, error_len)) return false;
     if (prefix->sealed)
         return q3_fail(error, error_len, "q3_prefix_prefill_layer: prefix already sealed");
     if (layer >= rt->cfg.num_layers)
@@ -969,6 +975,7 @@ extern "C" bool q3_suffix_attention_layer(q3_pack_plan *plan, uint32_t layer,
     if (!plan || !q || !k || !v || !out)
         return q3_fail(error, error_len, "q3_suffix_attention_layer: invalid argument");
     q3_attn_runtime *rt = plan->prefix->rt;
+    if (!q3_use_device(rt, error, error_len)) return false;
     if (layer >= rt->cfg.num_layers)
         return q3_fail(error, error_len, "q3_suffix_attention_layer: layer out of range");
     const q3_stage *st = plan->stage;
@@ -994,6 +1001,7 @@ extern "C" bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t 
             return q3_fail(error, error_len,
                            "q3_suffix_attention_layer_gathered: invalid argument");
     q3_attn_runtime *rt = plan->prefix->rt;
+    if (!q3_use_device(rt, error, error_len)) return false;
     if (layer >= rt->cfg.num_layers)
         return q3_fail(error, error_len,
                        "q3_suffix_attention_layer_gathered: layer out of range");
@@ -1267,6 +1275,7 @@ extern "C" bool q3_decode_attention_layer(q3_decode_plan *plan, uint32_t layer,
     if (!plan || !q || !out || ((k_new == NULL) != (v_new == NULL)))
         return q3_fail(error, error_len, "q3_decode_attention_layer: invalid argument");
     q3_attn_runtime *rt = plan->rt;
+    if (!q3_use_device(rt, error, error_len)) return false;
     if (layer >= rt->cfg.num_layers)
         return q3_fail(error, error_len, "q3_decode_attention_layer: layer out of range");
     if (k_new && !plan->can_append)

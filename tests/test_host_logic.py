@@ -155,3 +155,20 @@ def test_kv_bytes_accounting(pkg):
     # ref: src/q3_decide.cu:54-59 (fp32 K+V); the 129-token prefix of the
     # reference's report is 67,633,152 B
     assert pkg.lib().q3_kv_bytes_for_tokens(129, 64, 8, 128) == 67633152
+
+
+def test_decode_work_covers_every_page_once(pkg):
+    """q3_decode_work_host: every sequence is cut into chunks of at most 64 pages
+    that tile its page list exactly; slots are consecutive."""
+    ctx = np.asarray([1, 16, 17, 1024, 1025, 16384, 5000], np.uint32)
+    work, swb = pkg.decode_work_host(ctx)
+    assert swb[0] == 0 and swb[-1] == len(work)
+    for s, c in enumerate(ctx):
+        chunks = work[swb[s]:swb[s + 1]]
+        assert len(chunks) >= 1 and all(ch[0] == s for ch in chunks)
+        pages = (int(c) + 15) // 16
+        assert chunks[0][1] == 0 and chunks[-1][2] == pages
+        for a, b in zip(chunks, chunks[1:]):
+            assert a[2] == b[1]
+        assert all(0 < ch[2] - ch[1] <= 64 for ch in chunks)
+    assert work[:, 3].tolist() == list(range(len(work)))
