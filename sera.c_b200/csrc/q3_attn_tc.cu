@@ -752,7 +752,7 @@ __global__ void gather_wait_kernel(const uint32_t *flags, uint32_t n_ranks, uint
                                    uint32_t *status) {
     const uint32_t r = threadIdx.x;
     if (r >= n_ranks) return;
-    for (uint32_t i = 0; i < (1u << 24); i++) {
+    for (uint32_t i = 0; i < (1u << 20); i++) {   /* about a second */
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
         if ((int32_t)(v - seq) >= 0) return;

@@ -228,6 +228,59 @@ def test_host_buffer_entry_pipelined(pkg):
     rt.close()
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_random_ragged_batches(pkg, seed):
+    """Randomly shaped batches: prefix lengths around page and tile boundaries,
+    1..9 branches of 1..70 tokens under scattered handles, 1-4 KV heads."""
+    rng = np.random.default_rng(100 + seed)
+    P = int(rng.choice([1, 15, 16, 17, 127, 128, 129, 255, 300, 513]))
+    nb = int(rng.integers(1, 10))
+    lens = [int(x) for x in rng.integers(1, 71, nb)]
+    handles = [int(x) for x in rng.permutation(nb + 3)[:nb]]
+    hkv = int(rng.choice([1, 2, 4]))
+    case = harness.rounded_case(_cases.Case("rand%d" % seed, P, lens, n_heads=8 * hkv,
+                                            n_kv_heads=hkv, seed=seed,
+                                            unit_norm_weights=bool(seed % 2),
+                                            branch_handles=handles))
+    ref = oracle.run_case(case)["out"]
+    got = harness.run_case_native(pkg, case, out_fp32=True, seed=seed)
+    assert np.abs(got - ref).max() <= ATOL
+    assert np.array_equal(_candidate_argmax(got, case), _candidate_argmax(ref, case))
+
+
+def test_suffix_at_default_cap(pkg):
+    """One branch at the reference's default suffix capacity (512 tokens,
+    ref: src/q3_decide.h:25) next to short ones."""
+    case = harness.rounded_case(_cases.Case("cap", 64, [512, 2, 31], n_heads=8, n_kv_heads=1,
+                                            seed=9))
+    ref = oracle.run_case(case)["out"]
+    got = harness.run_case_native(pkg, case, out_fp32=True)
+    assert np.abs(got - ref).max() <= ATOL
+
+
+def test_bounded_wait_reports_instead_of_hanging(pkg):
+    """A device-side wait whose flag nobody sets gives up after about a second
+    and reports through the status word; the context stays usable."""
+    import ctypes
+    rt = pkg.Runtime(num_layers=1, n_heads=8, n_kv_heads=1, max_positions=64,
+                     max_tokens=16, num_pages=8)
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    buf = torch.zeros(16, dtype=torch.bfloat16, device="cuda")
+    peers = pkg.GatherPeers()
+    peers.n_ranks, peers.rank = 2, 0
+    for r in range(2):
+        peers.gathered[r] = buf.data_ptr()
+        peers.flags[r] = flags.data_ptr()
+    flags[0] = 5                      # rank 0 "arrived", rank 1 never does
+    torch.cuda.synchronize()
+    rt.wait_gathered(peers, 5)
+    with pytest.raises(pkg.Q3Error, match="gave up a bounded wait"):
+        rt.synchronize()
+    assert rt.stats().device_status & 2
+    assert int(flags.sum().item()) == 5          # the device still answers
+    rt.close()
+
+
 def test_error_paths(pkg):
     rt = pkg.Runtime(num_layers=1, n_heads=8, n_kv_heads=1, max_positions=256,
                      max_tokens=32, num_pages=12)
