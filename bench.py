@@ -188,21 +188,22 @@ def run_ours(args):
 
     fused = world > 1 and args.gather == "fused"
     pg = sharding.PeerGather(TOKENS, hq, D, torch.bfloat16, device) if fused else None
-    seq_base = [0]
 
     def step_device():
         if fused:
             # attention kernels store their rows into every rank's gathered
             # buffer; buffer b is reused by layer l+2 only after every rank
             # has seen layer l complete (device-side flag wait, no collective)
-            s0 = seq_base[0]
+            # sequence numbers are step-relative; the device-side counter
+            # advanced at the end makes every step (or graph replay) publish
+            # fresh ones
             for l in range(L):
                 if l >= 2:
-                    rt.wait_gathered(pg.peers(l), s0 + l - 1)
-                plan.attention_layer_gathered(l, dq_[l], dk_[l], dv_[l], pg.peers(l), s0 + l + 1)
-            rt.wait_gathered(pg.peers(L - 2), s0 + L - 1)
-            rt.wait_gathered(pg.peers(L - 1), s0 + L)
-            seq_base[0] = s0 + L
+                    rt.wait_gathered(pg.peers(l), l - 1)
+                plan.attention_layer_gathered(l, dq_[l], dk_[l], dv_[l], pg.peers(l), l + 1)
+            rt.wait_gathered(pg.peers(L - 2), L - 1)
+            rt.wait_gathered(pg.peers(L - 1), L)
+            rt.gather_advance(L)
             return
         works = [None, None]
         for l in range(L):
@@ -228,6 +229,7 @@ def run_ours(args):
 
     def timed(fn, steps, warmup, drain=None):
         with torch.cuda.stream(stream):
+            barrier()     # ranks enter together: the device-side gather waits are bounded (~1 s)
             for _ in range(warmup):
                 fn()
             barrier()
@@ -255,8 +257,27 @@ def run_ours(args):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms, phases, launches = timed(step_device, args.steps, args.warmup)
-    clocks = sampler.stop() if sampler else None
+    use_graph = args.graph == "on"
+    if use_graph and world > 1 and args.gather == "nccl":
+        raise SystemExit("--graph on records this library's calls only: use --gather fused|none")
+    if use_graph:
+        # the 64-layer step recorded once and replayed as one graph launch;
+        # per-kernel times then come from a short eager pass after the timed region
+        with torch.cuda.stream(stream):
+            barrier()
+            for _ in range(2):
+                step_device()
+            barrier()
+            rt.graph_begin()
+            step_device()
+            graph = rt.graph_end()
+        ms, _, launches = timed(graph.launch, args.steps, args.warmup)
+        clocks = sampler.stop() if sampler else None
+        _, phases, _ = timed(step_device, args.steps, 1)
+        graph.close()
+    else:
+        ms, phases, launches = timed(step_device, args.steps, args.warmup)
+        clocks = sampler.stop() if sampler else None
     ms_e2e, _, _ = timed(step_host, max(1, min(args.steps, 3)), 1, drain=rt.synchronize)
     e2e_steps = max(1, min(args.steps, 3))
     rt.synchronize()
@@ -302,6 +323,9 @@ def run_ours(args):
                          "ms_per_launch": per_launch_ms, "launches": attn_n,
                          "flops_per_launch": flops_per_launch},
             "kernel_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
+            "launch_mode": ("one CUDA graph per step; per-kernel times from an eager pass "
+                            "of the same step after the timed region") if use_graph
+                           else "eager; per-kernel times from the timed region",
             "device_status": status,
         }
     for o in (plan, bset, prefix):
@@ -546,6 +570,8 @@ def main():
                     help="skip the single-layer prefill / cascade / decode lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--graph", default="off", choices=["on", "off"],
+                    help="record the 64-layer step once and replay it as one CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
                     help="per-layer output all-gather at N > 1: 'fused' = peer stores from "
                          "the attention epilogue (default), 'nccl' = all_gather_into_tensor "

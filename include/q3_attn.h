@@ -309,6 +309,27 @@ bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t layer,
                                         char *error, size_t error_len);
 bool q3_attn_wait_gathered(q3_attn_runtime *rt, const q3_gather_peers *gather,
                            uint32_t seq, char *error, size_t error_len);
+/* Every `seq` above is offset on the device by a per-runtime counter that
+ * starts at 0; this queues `counter += count` on the runtime's stream. A step
+ * recorded into a graph passes step-relative sequence numbers (1..L) and ends
+ * with q3_attn_gather_advance(rt, L), after the waits of its last layers, so
+ * that every replay publishes fresh numbers. All ranks must advance alike. */
+bool q3_attn_gather_advance(q3_attn_runtime *rt, uint32_t count, char *error,
+                            size_t error_len);
+
+/* --- replaying a fixed sequence of layer calls as one CUDA graph --------- *
+ * The reference notes CUDA-graph capture of the 64-layer stack as the natural
+ * next step of its launch plumbing (ref: docs/M3.md, src/q3_forward.cu:1588-1651
+ * launches every layer eagerly). Between begin and end, the layer calls of this
+ * header (device-pointer variants, including the gathered one) are recorded
+ * instead of executed; q3_attn_graph_launch replays them on the runtime's
+ * stream with the same pointers. Per-kernel timing is suspended while
+ * recording. The host-buffer entry point cannot be recorded. */
+typedef struct q3_attn_graph q3_attn_graph;
+bool q3_attn_graph_begin(q3_attn_runtime *rt, char *error, size_t error_len);
+q3_attn_graph *q3_attn_graph_end(q3_attn_runtime *rt, char *error, size_t error_len);
+bool q3_attn_graph_launch(q3_attn_graph *graph, char *error, size_t error_len);
+void q3_attn_graph_destroy(q3_attn_graph *graph);
 
 /* --- paged decode: many independent sequences, one query token each --- */
 typedef struct q3_decode_plan q3_decode_plan;

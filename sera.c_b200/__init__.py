@@ -155,6 +155,15 @@ class Runtime:
         _call(lib().q3_attn_phase_times, self.h, ms, n)
         return {name: (ms[i], int(n[i])) for i, name in enumerate(self.PHASES)}
 
+    def gather_advance(self, count):
+        _call(lib().q3_attn_gather_advance, self.h, count)
+
+    def graph_begin(self):
+        _call(lib().q3_attn_graph_begin, self.h)
+
+    def graph_end(self):
+        return Graph(_call(lib().q3_attn_graph_end, self.h))
+
     def wait_gathered(self, peers, seq):
         _call(lib().q3_attn_wait_gathered, self.h, ctypes.byref(peers), seq)
 
@@ -182,6 +191,21 @@ class Runtime:
         tokens = (q if q is not None else k).shape[0]
         _call(lib().q3_cuda_qknorm_rope_kvwrite, self.h, layer, _ptr(q), _ptr(k), _ptr(v),
               tokens, _ptr(rope_pos), _ptr(dst_page), _ptr(dst_slot), _ptr(q_out))
+
+
+class Graph:
+    """q3_attn_graph: a recorded sequence of layer calls, replayed as one launch."""
+
+    def __init__(self, handle):
+        self.h = handle
+
+    def launch(self):
+        _call(lib().q3_attn_graph_launch, self.h)
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().q3_attn_graph_destroy(self.h)
+            self.h = None
 
 
 class Prefix:

@@ -108,6 +108,11 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     sig("q3_suffix_attention_layer_gathered", b,
         [vp, u32, vp, vp, vp, ctypes.POINTER(GatherPeers), u32] + err)
     sig("q3_attn_wait_gathered", b, [vp, ctypes.POINTER(GatherPeers), u32] + err)
+    sig("q3_attn_gather_advance", b, [vp, u32] + err)
+    sig("q3_attn_graph_begin", b, [vp] + err)
+    sig("q3_attn_graph_end", vp, [vp] + err)
+    sig("q3_attn_graph_launch", b, [vp] + err)
+    sig("q3_attn_graph_destroy", None, [vp])
     sig("q3_decode_plan_create", vp, [vp, up, up, up, u32] + err)
     sig("q3_decode_plan_destroy", None, [vp])
     sig("q3_decode_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)

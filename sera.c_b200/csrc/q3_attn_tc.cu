@@ -736,8 +736,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
 /* After a layer's rows are stored: publish `seq` in every rank's flag array
  * (slot = this rank). One thread; the fence orders the flag after the rows of
  * the preceding kernels of this stream. */
-__global__ void gather_signal_kernel(const GatherFlags flags, uint32_t rank, uint32_t seq) {
+__global__ void gather_signal_kernel(const GatherFlags flags, uint32_t rank, uint32_t seq,
+                                     const uint32_t *epoch) {
     if (threadIdx.x == 0) {
+        seq += *epoch;
         __threadfence_system();
         for (uint32_t d = 0; d < flags.n; d++)
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.ptr[d] + rank),
@@ -749,9 +751,10 @@ __global__ void gather_signal_kernel(const GatherFlags flags, uint32_t rank, uin
 /* Wait (bounded) until every rank has published at least `seq` in this rank's
  * flag array, i.e. the gathered buffer holds that layer from every rank. */
 __global__ void gather_wait_kernel(const uint32_t *flags, uint32_t n_ranks, uint32_t seq,
-                                   uint32_t *status) {
+                                   const uint32_t *epoch, uint32_t *status) {
     const uint32_t r = threadIdx.x;
     if (r >= n_ranks) return;
+    seq += *epoch;
     for (uint32_t i = 0; i < (1u << 20); i++) {   /* about a second */
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
@@ -761,14 +764,28 @@ __global__ void gather_wait_kernel(const uint32_t *flags, uint32_t n_ranks, uint
     atomicOr(status, Q3_STATUS_GATHER_TIMEOUT);
 }
 
+/* Sequence numbers of later calls start `count` higher: a recorded step passes
+ * step-relative numbers and ends with this. */
+__global__ void gather_advance_kernel(uint32_t *epoch, uint32_t count) {
+    if (threadIdx.x == 0) *epoch += count;
+}
+
 }  // namespace
+
+bool q3_launch_gather_advance(q3_attn_runtime *rt, uint32_t count, char *error,
+                              size_t error_len) {
+    gather_advance_kernel<<<1, 32, 0, rt->stream>>>(rt->gather_epoch_dev, count);
+    Q3_LAUNCH_CHECK("gather_advance launch failed");
+    rt->n_launch++;
+    return true;
+}
 
 bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
                              cudaStream_t stream, char *error, size_t error_len) {
     GatherFlags f;
     f.n = g->n_ranks;
     for (uint32_t d = 0; d < g->n_ranks; d++) f.ptr[d] = g->flags[d];
-    gather_signal_kernel<<<1, 32, 0, stream>>>(f, g->rank, seq);
+    gather_signal_kernel<<<1, 32, 0, stream>>>(f, g->rank, seq, rt->gather_epoch_dev);
     Q3_LAUNCH_CHECK("gather_signal launch failed");
     rt->n_launch++;
     return true;
@@ -777,7 +794,7 @@ bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint
 bool q3_launch_gather_wait(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
                            char *error, size_t error_len) {
     gather_wait_kernel<<<1, 32, 0, rt->stream>>>(g->flags[g->rank], g->n_ranks, seq,
-                                                 rt->status_dev);
+                                                 rt->gather_epoch_dev, rt->status_dev);
     Q3_LAUNCH_CHECK("gather_wait launch failed");
     rt->n_launch++;
     return true;

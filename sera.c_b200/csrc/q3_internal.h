@@ -82,6 +82,7 @@ struct q3_attn_runtime {
     uint32_t dec_slots;
 
     uint32_t *status_dev;
+    uint32_t *gather_epoch_dev;  /* added to every gather sequence number on the device */
     uint32_t *status_host; /* pinned mirror, refreshed by q3_attn_synchronize */
 
     /* pinned staging for the host-buffer entry point (grow-once) */
@@ -99,6 +100,10 @@ struct q3_attn_runtime {
     cudaEvent_t ev_gather[4];
     bool gather_ready;
     uint64_t gather_calls;
+    /* stream capture (q3_attn_graph_*) */
+    bool capturing;
+    bool capture_used_gather;
+    uint64_t capture_launches;
 
     uint64_t n_alloc, n_free, n_sync, n_launch;
     uint64_t workspace_bytes;
@@ -116,17 +121,24 @@ enum { Q3_PHASE_KVWRITE = 0, Q3_PHASE_ATTENTION = 1, Q3_PHASE_MERGE = 2,
        Q3_PHASE_DECODE = 3, Q3_PHASE_COUNT = 4 };
 
 static inline void q3_phase_begin(q3_attn_runtime *rt, int phase) {
-    if (rt->timing_on && rt->ev_used < rt->ev_phase.size()) {
+    if (rt->timing_on && !rt->capturing && rt->ev_used < rt->ev_phase.size()) {
         rt->ev_phase[rt->ev_used] = (uint8_t)phase;
         cudaEventRecord(rt->ev[2 * rt->ev_used], rt->stream);
     }
 }
 static inline void q3_phase_end(q3_attn_runtime *rt) {
-    if (rt->timing_on && rt->ev_used < rt->ev_phase.size()) {
+    if (rt->timing_on && !rt->capturing && rt->ev_used < rt->ev_phase.size()) {
         cudaEventRecord(rt->ev[2 * rt->ev_used + 1], rt->stream);
         rt->ev_used++;
     }
 }
+
+struct q3_attn_graph {
+    q3_attn_runtime *rt;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    uint64_t launches;   /* kernels per replay */
+};
 
 struct q3_prefix_kv {
     q3_attn_runtime *rt;
@@ -214,6 +226,8 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer,
                          size_t error_len);
 bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
                              cudaStream_t stream, char *error, size_t error_len);
+bool q3_launch_gather_advance(q3_attn_runtime *rt, uint32_t count, char *error,
+                              size_t error_len);
 bool q3_launch_gather_wait(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
                            char *error, size_t error_len);
 bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer,

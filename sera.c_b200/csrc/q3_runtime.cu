@@ -163,6 +163,7 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     rt->dec_ml = nullptr;
     rt->dec_slots = 0;
     rt->status_dev = nullptr;
+    rt->gather_epoch_dev = nullptr;
     rt->status_host = nullptr;
     rt->host_stage = rt->dev_stage = nullptr;
     rt->host_stage_bytes = rt->dev_stage_bytes = 0;
@@ -172,6 +173,9 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     rt->gather_stream = nullptr;
     rt->gather_ready = false;
     rt->gather_calls = 0;
+    rt->capturing = false;
+    rt->capture_used_gather = false;
+    rt->capture_launches = 0;
     rt->n_alloc = rt->n_free = rt->n_sync = rt->n_launch = 0;
     rt->workspace_bytes = 0;
     rt->timing_on = false;
@@ -195,6 +199,7 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     ok = ok && rt_malloc(rt, (void **)&rt->qk_norm_w, w_bytes) == cudaSuccess;
     ok = ok && rt_malloc(rt, (void **)&rt->rope_table, rope_bytes) == cudaSuccess;
     ok = ok && rt_malloc(rt, (void **)&rt->status_dev, sizeof(uint32_t)) == cudaSuccess;
+    ok = ok && rt_malloc(rt, (void **)&rt->gather_epoch_dev, sizeof(uint32_t)) == cudaSuccess;
     ok = ok && cudaHostAlloc((void **)&rt->status_host, sizeof(uint32_t),
                              cudaHostAllocDefault) == cudaSuccess;
     if (!ok) {
@@ -210,6 +215,7 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     cudaMemsetAsync(rt->v_pool, 0, pool_bytes, rt->stream);
     cudaMemsetAsync(rt->q2, 0, q2_bytes, rt->stream);
     cudaMemsetAsync(rt->status_dev, 0, sizeof(uint32_t), rt->stream);
+    cudaMemsetAsync(rt->gather_epoch_dev, 0, sizeof(uint32_t), rt->stream);
     cudaMemsetAsync(rt->fix_counters, 0, (size_t)rt->part_slots * 8 * sizeof(uint32_t),
                     rt->stream);
 
@@ -276,6 +282,7 @@ extern "C" void q3_attn_destroy(q3_attn_runtime *rt) {
     rt_free(rt, rt->qk_norm_w);
     rt_free(rt, rt->rope_table);
     rt_free(rt, rt->status_dev);
+    rt_free(rt, rt->gather_epoch_dev);
     rt_free(rt, rt->dev_stage);
     for (cudaEvent_t e : rt->ev) cudaEventDestroy(e);
     if (rt->gather_ready) {
@@ -1031,6 +1038,7 @@ extern "C" bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t 
                            "q3_suffix_attention_layer_gathered: stream set-up failed");
         rt->gather_ready = true;
     }
+    if (rt->capturing) rt->capture_used_gather = true;
     cudaEvent_t ev = rt->ev_gather[rt->gather_calls++ % 4];
     cudaError_t e = cudaEventRecord(ev, rt->stream);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(rt->gather_stream, ev, 0);
@@ -1051,6 +1059,13 @@ extern "C" bool q3_attn_wait_gathered(q3_attn_runtime *rt, const q3_gather_peers
         gather->rank >= gather->n_ranks || !gather->flags[gather->rank])
         return q3_fail(error, error_len, "q3_attn_wait_gathered: invalid argument");
     return q3_launch_gather_wait(rt, gather, seq, error, error_len);
+}
+
+extern "C" bool q3_attn_gather_advance(q3_attn_runtime *rt, uint32_t count, char *error,
+                                       size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt) return q3_fail(error, error_len, "q3_attn_gather_advance: null runtime");
+    return q3_launch_gather_advance(rt, count, error, error_len);
 }
 
 extern "C" bool q3_cuda_qknorm_rope_kvwrite(q3_attn_runtime *rt, uint32_t layer,
@@ -1084,6 +1099,9 @@ extern "C" bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t laye
         return q3_fail(error, error_len,
                        "q3_suffix_attention_layer_host: invalid argument");
     q3_attn_runtime *rt = plan->prefix->rt;
+    if (rt->capturing)
+        return q3_fail(error, error_len,
+                       "q3_suffix_attention_layer_host: cannot be recorded into a graph");
     const size_t qb = (size_t)plan->tokens * rt->cfg.n_heads * Q3_D * 2;
     const size_t kb = (size_t)plan->tokens * rt->cfg.n_kv_heads * Q3_D * 2;
     const size_t ob = rt->cfg.out_fp32 ? 2 * qb : qb;
@@ -1144,6 +1162,87 @@ extern "C" bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t laye
     if (e != cudaSuccess)
         return q3_fail_cuda(error, error_len, "q3_suffix_attention_layer_host: D2H", e);
     return true;
+}
+
+/* ---------------------------------------------------------------------- */
+/* graph capture of a sequence of layer calls                              */
+/* ---------------------------------------------------------------------- */
+
+extern "C" bool q3_attn_graph_begin(q3_attn_runtime *rt, char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt) return q3_fail(error, error_len, "q3_attn_graph_begin: null runtime");
+    if (rt->capturing) return q3_fail(error, error_len, "q3_attn_graph_begin: already recording");
+    if (!q3_use_device(rt, error, error_len)) return false;
+    cudaError_t e = cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeRelaxed);
+    if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "q3_attn_graph_begin", e);
+    rt->capturing = true;
+    rt->capture_used_gather = false;
+    rt->capture_launches = rt->n_launch;
+    return true;
+}
+
+extern "C" q3_attn_graph *q3_attn_graph_end(q3_attn_runtime *rt, char *error,
+                                            size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt || !rt->capturing) {
+        q3_fail(error, error_len, "q3_attn_graph_end: not recording");
+        return NULL;
+    }
+    cudaError_t e = cudaSuccess;
+    if (rt->capture_used_gather) {
+        /* join the side stream back, or the capture has unjoined work */
+        cudaEvent_t ev = rt->ev_gather[rt->gather_calls++ % 4];
+        e = cudaEventRecord(ev, rt->gather_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(rt->stream, ev, 0);
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e2 = cudaStreamEndCapture(rt->stream, &graph);
+    rt->capturing = false;
+    if (e == cudaSuccess) e = e2;
+    if (e != cudaSuccess || !graph) {
+        q3_fail_cuda(error, error_len, "q3_attn_graph_end", e);
+        if (graph) cudaGraphDestroy(graph);
+        return NULL;
+    }
+    q3_attn_graph *g = new (std::nothrow) q3_attn_graph();
+    if (!g) {
+        cudaGraphDestroy(graph);
+        q3_fail(error, error_len, "q3_attn_graph_end: allocation failed");
+        return NULL;
+    }
+    g->rt = rt;
+    g->graph = graph;
+    g->exec = nullptr;
+    g->launches = rt->n_launch - rt->capture_launches;
+    rt->n_launch = rt->capture_launches;   /* nothing ran while recording */
+    e = cudaGraphInstantiate(&g->exec, graph, 0);
+    if (e != cudaSuccess) {
+        q3_fail_cuda(error, error_len, "q3_attn_graph_end: instantiate", e);
+        cudaGraphDestroy(graph);
+        delete g;
+        return NULL;
+    }
+    return g;
+}
+
+extern "C" bool q3_attn_graph_launch(q3_attn_graph *g, char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!g || !g->exec) return q3_fail(error, error_len, "q3_attn_graph_launch: null graph");
+    if (g->rt->capturing)
+        return q3_fail(error, error_len, "q3_attn_graph_launch: runtime is recording");
+    if (!q3_use_device(g->rt, error, error_len)) return false;
+    cudaError_t e = cudaGraphLaunch(g->exec, g->rt->stream);
+    if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "q3_attn_graph_launch", e);
+    g->rt->n_launch += g->launches;
+    return true;
+}
+
+extern "C" void q3_attn_graph_destroy(q3_attn_graph *g) {
+    if (!g) return;
+    if (g->rt && g->rt->stream) cudaStreamSynchronize(g->rt->stream);
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
 }
 
 /* ---------------------------------------------------------------------- */

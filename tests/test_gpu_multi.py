@@ -58,6 +58,28 @@ def _worker(rank, world, port, ret):
             want = sharding.gathered_to_full(gathered).float().cpu().numpy()
             ok = ok and np.array_equal(got, want)
             dist.barrier()
+        # the same exchange recorded as a graph with step-relative sequence
+        # numbers and replayed: flags left by one replay must not satisfy the next
+        rt.synchronize()
+        dist.barrier()
+        rt.gather_advance(3)                     # past the numbers used above
+        rt.graph_begin()
+        for it in range(2):
+            plan.attention_layer_gathered(1, q, k, v, pg.peers(it), it + 1)
+        rt.wait_gathered(pg.peers(0), 1)
+        rt.wait_gathered(pg.peers(1), 2)
+        rt.gather_advance(2)
+        graph = rt.graph_end()
+        for rep in range(3):
+            pg.bufs[0].zero_(); pg.bufs[1].zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph.launch()
+            rt.synchronize()
+            for it in range(2):
+                ok = ok and np.array_equal(pg.full(it).float().cpu().numpy(), want)
+            dist.barrier()
+        graph.close()
     ok = ok and rt.stats().device_status == 0
     ret[rank] = bool(ok)
     for o in (plan, bset, prefix):

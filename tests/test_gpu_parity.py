@@ -228,6 +228,48 @@ def test_host_buffer_entry_pipelined(pkg):
     rt.close()
 
 
+def test_graph_replay_equals_eager(pkg):
+    """q3_attn_graph_*: two layer calls recorded once and replayed; every
+    replay gives the rows of the eager calls, also after the inputs changed
+    in place (the graph holds pointers, not data)."""
+    case = harness.rounded_case(_cases.make_case("ragged"))
+    _, rt, prefix, bset, plan = harness.run_case_native(pkg, case, return_runtime=True)
+    S = case.S
+    g = torch.Generator().manual_seed(5)
+    mk = lambda h: torch.randn(S, h, case.D, generator=g).to(torch.bfloat16).cuda()
+    q, k, v = mk(case.H), mk(case.Hkv), mk(case.Hkv)
+    o = [torch.zeros(S, case.H, case.D, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    e = [torch.zeros_like(o[0]) for _ in range(2)]
+    host = [t.cpu().pin_memory() for t in (q, k, v, o[0])]
+    torch.cuda.synchronize()
+    launches0 = rt.stats().kernel_launches
+    rt.graph_begin()
+    plan.attention_layer(0, q, k, v, o[0])
+    plan.attention_layer(1, q, k, v, o[1])
+    with pytest.raises(pkg.Q3Error, match="cannot be recorded"):
+        plan.attention_layer_host(0, *host)
+    graph = rt.graph_end()
+    rt.synchronize()
+    assert rt.stats().kernel_launches == launches0      # recording runs nothing
+    assert float(o[0].abs().max()) == 0.0
+    for rep in range(3):
+        graph.launch()
+        rt.synchronize()
+        plan.attention_layer(0, q, k, v, e[0])
+        plan.attention_layer(1, q, k, v, e[1])
+        rt.synchronize()
+        assert torch.equal(o[0], e[0]) and torch.equal(o[1], e[1]), rep
+        assert float(o[0].float().abs().max()) > 0.0
+        q.copy_(mk(case.H)); k.copy_(mk(case.Hkv)); v.copy_(mk(case.Hkv))
+        torch.cuda.synchronize()
+    assert rt.stats().kernel_launches == launches0 + 3 * 4 + 3 * 4
+    assert rt.stats().device_status == 0
+    graph.close()
+    for x in (plan, bset, prefix):
+        x.close()
+    rt.close()
+
+
 @pytest.mark.parametrize("seed", [0, 1, 2, 3])
 def test_random_ragged_batches(pkg, seed):
     """Randomly shaped batches: prefix lengths around page and tile boundaries,
