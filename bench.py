@@ -527,6 +527,164 @@ def cpu_baseline(target_s=15.0):
                       % (L, nb, BRANCHES, SUFFIX, PREFIX, t)}
 
 
+def reference_gpu_kernels():
+    """The reference's own CUDA kernels (compiled unchanged for sm_100a into
+    oracle/_ref/libq3ref.so) timed on this box in their own layout (fp32
+    contiguous slabs): prefill at 4096 tokens, the 8192-token-prefix cascade
+    case and one layer of the 64-layer workload. Reported beside the CPU number
+    of the reference arm; none of this repository's kernels run here."""
+    import ctypes
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _gpu_harness as harness
+    path = os.path.join(ROOT, "oracle", "_ref", "libq3ref.so")
+    if not torch.cuda.is_available() or not os.path.exists(path):
+        return {"unavailable": "no GPU or oracle/_ref/libq3ref.so not built"}
+    R = harness.fp32_surface(path)
+    err = ctypes.create_string_buffer(256)
+    f32 = torch.float32
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    scale = float(1.0 / np.sqrt(D))
+    ifr = torch.tensor((1.0 / (1e6 ** (np.arange(D // 2) * 2.0 / D))).astype(np.float32),
+                       device=dev)
+    ones = torch.ones(D, dtype=f32, device=dev)
+
+    def p(t):
+        return ctypes.c_void_p(t.data_ptr())
+
+    def ck(ok):
+        if not ok:
+            raise RuntimeError(err.value.decode())
+
+    def timeit(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    res = {}
+    # prefill: rms_norm(q), rms_norm(k), rope, attention over the call's own rows
+    T = 4096
+    q = torch.randn(T, H, D, generator=g, dtype=f32, device=dev)
+    k = torch.randn(T, HKV, D, generator=g, dtype=f32, device=dev)
+    v = torch.randn(T, HKV, D, generator=g, dtype=f32, device=dev)
+    out = torch.zeros_like(q)
+
+    def prefill():
+        ck(R.q3_cuda_rms_norm(p(q), p(ones), T * H, D, 1e-6, p(q), None, err, 256))
+        ck(R.q3_cuda_rms_norm(p(k), p(ones), T * HKV, D, 1e-6, p(k), None, err, 256))
+        ck(R.q3_cuda_rope(p(q), p(k), T, H, HKV, D, 0, p(ifr), None, err, 256))
+        ck(R.q3_cuda_attention(p(q), p(k), p(v), T, H, HKV, D, 0, None, 0, scale, p(out),
+                               None, err, 256))
+    ms = timeit(prefill, 3)
+    pairs = T * (T + 1) // 2
+    res["prefill_4096"] = {"ms": ms, "tflops": 4 * D * H * pairs / (ms * 1e-3) / 1e12,
+                           "tokens_per_s": T / (ms * 1e-3)}
+    del q, k, v, out
+
+    def cascade(P, B, n, reps):
+        S = B * n
+        qs = torch.randn(S, H, D, generator=g, dtype=f32, device=dev)
+        ks = torch.randn(S, HKV, D, generator=g, dtype=f32, device=dev)
+        pk = torch.randn(1, P, HKV, D, generator=g, dtype=f32, device=dev)
+        pv = torch.randn(1, P, HKV, D, generator=g, dtype=f32, device=dev)
+        sk = torch.randn(B, 1, n, HKV * D, generator=g, dtype=f32, device=dev)
+        sv = torch.randn(B, 1, n, HKV * D, generator=g, dtype=f32, device=dev)
+        tb = torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(n)
+        tl = torch.arange(n, dtype=torch.int32, device=dev).repeat(B)
+        pos = (tl + P).to(torch.int32)
+        o = torch.zeros_like(qs)
+
+        def run():
+            ck(R.q3_cuda_rms_norm(p(qs), p(ones), S * H, D, 1e-6, p(qs), None, err, 256))
+            ck(R.q3_cuda_rms_norm(p(ks), p(ones), S * HKV, D, 1e-6, p(ks), None, err, 256))
+            ck(R.q3_cuda_rope_positions(p(qs), p(ks), S, H, HKV, D, p(pos), p(ifr), None,
+                                        err, 256))
+            ck(R.q3_cuda_attention_segmented(p(qs), p(pk), p(pv), P, P, p(sk), p(sv), n, 1, 0,
+                                             p(tb), p(tl), S, H, HKV, D, scale, p(o), None,
+                                             err, 256))
+        ms = timeit(run, reps)
+        pairs = S * P + B * n * (n + 1) // 2
+        return {"ms": ms, "tflops": 4 * D * H * pairs / (ms * 1e-3) / 1e12,
+                "suffix_tokens_per_s": S / (ms * 1e-3)}
+    res["cascade_p8192_b64x24"] = cascade(8192, 64, 24, 3)
+    res["stack_layer_p32768_b128x16"] = cascade(PREFIX, BRANCHES, SUFFIX, 2)
+    res["stack64_tokens_per_s_extrapolated"] = TOKENS / (
+        res["stack_layer_p32768_b128x16"]["ms"] * 1e-3 * L)
+    res["note"] = ("reference SIMT kernels, fp32 contiguous KV, norm + rope + attention per "
+                   "call, scatter of the suffix rows not timed (file-static in the reference)")
+    return res
+
+
+def python_path_baseline():
+    """The reference's Python path for this arithmetic: the HuggingFace Qwen3
+    functions its oracle scripts execute (RMSNorm, rotary embedding,
+    apply_rotary_pos_emb, repeat_kv) plus torch SDPA, on CPU in fp32 with all
+    host threads (ref: tools/qwen3_q4_oracle.py:88-92,151-154). Prefill at 4096
+    tokens and the 8192-token-prefix cascade case, one repeat each after a
+    warm-up on a tenth of the size."""
+    try:
+        import torch
+        from transformers.models.qwen3 import modeling_qwen3 as m
+        from transformers.models.qwen3.configuration_qwen3 import Qwen3Config
+    except Exception as e:  # the third-party modules are not part of this repository
+        return {"unavailable": "transformers/torch import failed: %s" % e}
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = Qwen3Config(hidden_size=H * D, num_attention_heads=H, num_key_value_heads=HKV,
+                      head_dim=D, rope_theta=1e6, max_position_embeddings=1 << 17,
+                      num_hidden_layers=1, intermediate_size=64, vocab_size=16)
+    qn, kn, rot = m.Qwen3RMSNorm(D, eps=1e-6), m.Qwen3RMSNorm(D, eps=1e-6), m.Qwen3RotaryEmbedding(cfg)
+    gen = torch.Generator().manual_seed(0)
+
+    def run(P, B, n):
+        """P resident-equivalent prefix tokens + B branches of n tokens; B == 0: causal prefill of P."""
+        T = P + B * n
+        q = torch.randn(1, T, H, D, generator=gen)
+        k = torch.randn(1, T, HKV, D, generator=gen)
+        v = torch.randn(1, T, HKV, D, generator=gen)
+        pos = torch.cat([torch.arange(P)] + [torch.arange(P, P + n)] * B)[None]
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            rows = slice(0, T) if B == 0 else slice(P, T)   # cascade: only the suffix rows query
+            qs = qn(q[:, rows]).transpose(1, 2)
+            ks = kn(k).transpose(1, 2)
+            vs = v.transpose(1, 2)
+            cos, sin = rot(vs, pos)
+            qs, _ = m.apply_rotary_pos_emb(qs, qs, cos[:, rows], sin[:, rows])
+            ks, _ = m.apply_rotary_pos_emb(ks, ks, cos, sin)
+            kk, vv = m.repeat_kv(ks, H // HKV), m.repeat_kv(vs, H // HKV)
+            if B == 0:
+                torch.nn.functional.scaled_dot_product_attention(qs, kk, vv, is_causal=True)
+            else:
+                S = B * n
+                br = torch.arange(S) // n
+                lp = torch.arange(S) % n
+                mask = torch.zeros(S, T, dtype=torch.bool)
+                mask[:, :P] = True
+                mask[:, P:] = (br[:, None] == br[None, :]) & (lp[None, :] <= lp[:, None])
+                torch.nn.functional.scaled_dot_product_attention(qs, kk, vv, attn_mask=mask)
+        return time.perf_counter() - t0
+
+    res = {"cores": torch.get_num_threads()}
+    run(400, 0, 0)
+    t = run(4096, 0, 0)
+    res["prefill_4096"] = {"ms": t * 1e3, "tokens_per_s": 4096 / t,
+                           "tflops": 4 * D * H * (4096 * 4097 // 2) / t / 1e12}
+    run(800, 8, 24)
+    t = run(8192, 64, 24)
+    res["cascade_p8192_b64x24"] = {
+        "ms": t * 1e3, "suffix_tokens_per_s": 1536 / t,
+        "tflops": 4 * D * H * (1536 * 8192 + 64 * 300) / t / 1e12,
+        "note": "includes norm + rope of the 8192 prefix keys, which the GPU path keeps resident"}
+    return res
+
+
 def run_reference(args):
     """The reference arm: the path's CPU implementation (the oracle port of the
     reference kernels; the reference ships no CPU attention of its own) on all
@@ -557,7 +715,9 @@ def run_reference(args):
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
-        "gpu_launches": 0}))
+        "gpu_launches": 0,
+        **({} if args.no_ref_gpu else {"reference_gpu_kernels": reference_gpu_kernels(),
+                                       "python_path_cpu": python_path_baseline()})}))
 
 
 def main():
@@ -570,6 +730,8 @@ def main():
                     help="skip the single-layer prefill / cascade / decode lines")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--no-ref-gpu", action="store_true",
+                    help="--impl reference: skip timing the reference's own CUDA kernels")
     ap.add_argument("--graph", default="off", choices=["on", "off"],
                     help="record the 64-layer step once and replay it as one CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
