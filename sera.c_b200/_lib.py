@@ -1,4 +1,4 @@
-"""ctypes signatures for every symbol include/q3_attn.h declares."""
+"""ctypes signatures for every symbol include/q3_attn.h and include/q3_q4_linear.h declare."""
 import ctypes
 import os
 
@@ -12,6 +12,47 @@ class Q3Error(RuntimeError):
 
 def lib_path():
     return os.path.join(PKG, "libq3attn.so")
+
+
+class LinearGeometry(ctypes.Structure):
+    """q3_q4_linear_geometry"""
+    _fields_ = [("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
+                ("qtype", ctypes.c_uint32), ("weight_bytes", ctypes.c_uint64)]
+
+
+class LinearStats(ctypes.Structure):
+    """q3_q4_linear_stats"""
+    _fields_ = [("total_ms", ctypes.c_double), ("activation_quant_ms", ctypes.c_double),
+                ("kernel_ms", ctypes.c_double), ("weight_bytes", ctypes.c_uint64),
+                ("activation_read_bytes", ctypes.c_uint64),
+                ("activation_write_bytes", ctypes.c_uint64),
+                ("kernel_launches", ctypes.c_uint64), ("cuda_allocations", ctypes.c_uint64),
+                ("host_syncs", ctypes.c_uint64)]
+
+
+def bind_linear(L):
+    """Signatures of include/q3_q4_linear.h (also valid for a build of the
+    reference's own q3_q4_linear, which exports part 1 under the same names)."""
+    vp, u32, sz, b = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_size_t, ctypes.c_bool
+    err = [ctypes.c_char_p, sz]
+    gp, sp = ctypes.POINTER(LinearGeometry), ctypes.POINTER(LinearStats)
+
+    def sig(name, res, args):
+        f = getattr(L, name, None)
+        if f is not None:
+            f.restype = res
+            f.argtypes = args
+
+    sig("q3_q4_linear_bind_geometry", b, [u32, u32, u32, gp] + err)
+    sig("q3_cuda_q4k_linear_init", b, [ctypes.c_int, sz, ctypes.c_int64, ctypes.c_int64] + err)
+    sig("q3_cuda_q4k_linear_workspace_bytes", sz, [])
+    sig("q3_cuda_q4k_linear_set_workspace", b, [vp, sz] + err)
+    sig("q3_cuda_q4k_linear_path_for_batch", ctypes.c_char_p, [sz])
+    sig("q3_cuda_q4k_linear", b, [gp, vp, vp, sz, vp, vp, sp] + err)
+    sig("q3_cuda_q4k_linear_read_stats", None, [sp, vp])
+    sig("q3_cuda_q4k_linear_f16", b, [gp, vp, vp, sz, vp, u32, vp] + err)
+    sig("q3_cuda_q4k_linear_status", b, [vp, ctypes.POINTER(u32)] + err)
+    return L
 
 
 class GatherPeers(ctypes.Structure):
@@ -38,6 +79,7 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
         f.argtypes = args
         return f
 
+    bind_linear(L)
     # ---- part 1: reference surface
     sig("q3_kv_cache_init", vp, [u32, u32, u32, u32] + err)
     sig("q3_kv_cache_reserve", b, [vp, u32] + err)

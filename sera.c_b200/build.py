@@ -19,7 +19,7 @@ LIB = os.path.join(PKG, "libq3attn.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 SOURCES = ["q3_runtime.cu", "q3_kvwrite.cu", "q3_attn_tc.cu", "q3_attn_decode.cu",
-           "q3_compat_fp32.cu", "q3_sched.cpp", "q3_diag.cpp"]
+           "q3_compat_fp32.cu", "q3_q4k_linear.cu", "q3_sched.cpp", "q3_diag.cpp"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
          "-std=c++17", "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"),
          "-I" + CSRC]
@@ -33,7 +33,8 @@ def needs_build():
     if not os.path.exists(LIB):
         return True
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
-    deps += [os.path.join(ROOT, "include", "q3_attn.h"), os.path.abspath(__file__)]
+    deps += [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include"))]
+    deps.append(os.path.abspath(__file__))
     return _newest(deps) > os.path.getmtime(LIB)
 
 

@@ -248,6 +248,9 @@ static inline bool q3_use_device(const q3_attn_runtime *rt, char *error, size_t 
 bool q3_encode_tmap_2d(CUtensorMap *map, const void *base, uint64_t inner,
                        uint64_t rows, uint32_t box_inner, uint32_t box_rows,
                        char *error, size_t error_len);
+bool q3_encode_tmap_bytes_2d(CUtensorMap *map, const void *base, uint64_t row_bytes,
+                             uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
+                             char *error, size_t error_len);
 bool q3_encode_tmap_q(CUtensorMap *map, const void *base, uint32_t n_heads,
                       uint32_t tokens, char *error, size_t error_len);
 

@@ -78,6 +78,28 @@ bool q3_encode_tmap_2d(CUtensorMap *map, const void *base, uint64_t inner,
     return true;
 }
 
+/* 2-D byte tensor {row_bytes, rows}, no swizzle: rows of packed quantised
+ * blocks. box_bytes and row_bytes must be multiples of 16. */
+bool q3_encode_tmap_bytes_2d(CUtensorMap *map, const void *base, uint64_t row_bytes,
+                             uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
+                             char *error, size_t error_len) {
+    encode_tiled_fn fn = get_encode_fn();
+    if (!fn) return q3_fail(error, error_len, "cuTensorMapEncodeTiled unavailable");
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {box_bytes, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)base, dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        if (error && error_len)
+            snprintf(error, error_len, "cuTensorMapEncodeTiled(bytes) failed (%d)", (int)r);
+        return false;
+    }
+    return true;
+}
+
 /* Query workspace [tokens][n_heads][128] f16 viewed as {128, n_heads, tokens};
  * box {64, 8, 16}: 16 tokens x 8 heads of one KV group, half a head row. */
 bool q3_encode_tmap_q(CUtensorMap *map, const void *base, uint32_t n_heads,

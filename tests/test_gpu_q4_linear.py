@@ -1,0 +1,151 @@
+"""GPU parity tests of the resident Q4_K linear through the C ABI
+(include/q3_q4_linear.h) against the CPU oracle, and - where it was built -
+against the reference's own MMQ/MMVQ kernels run on the same inputs.
+
+Bars: against the oracle fed the same f16-rounded operands, relative L2 error
+< 1e-4 (fp32 accumulation order is the only difference); against the exact
+oracle (fp32 dequantisation, fp32 activations, double accumulation), relative
+L2 error < 1e-3 and cosine > 0.99999. The reference's own test accepts 1e-2
+and 0.999 (tests/test_q3_q4_linear.cu:364-372)."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import __graft_entry__ as entry
+import q3_quant_oracle as qo
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lin():
+    entry.build()
+    entry.load_package()
+    from sera_c_b200 import q4_linear
+    return q4_linear, q4_linear.Q4Linear(0, 4096, 10240, 8192)
+
+
+def _case(seed, M, N, K):
+    rng = np.random.default_rng(seed)
+    w = qo.q4k_weight(rng, N, K)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    return w, x
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 256), (4, 256, 512), (16, 128, 1024),
+                                   (100, 384, 768), (128, 128, 256), (129, 256, 512),
+                                   (300, 256, 1280), (513, 1024, 5120)])
+def test_f16_entry_matches_oracle(lin, M, N, K):
+    q4, L = lin
+    w, x = _case(M + N + K, M, N, K)
+    geo = q4.bind_geometry(K, N)
+    wd = torch.from_numpy(w).cuda()
+    xd = torch.from_numpy(x).cuda().to(torch.float16)
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        out = L.linear_f16(geo, wd, xd, out_dtype=dt)
+        assert L.status() == 0
+        got = out.float().cpu().numpy()
+        ref16 = qo.q4k_linear(w, x, operands="f16")
+        m = qo.linear_error_metrics(got, ref16)
+        tol = 1e-4 if dt == torch.float32 else (6e-3 if dt == torch.bfloat16 else 1e-3)
+        assert m["rel_l2"] < tol, (dt, m)
+        if dt == torch.float32:
+            exact = qo.linear_error_metrics(got, qo.q4k_linear(w, x))
+            assert exact["rel_l2"] < 1e-3 and exact["cos"] > 0.99999, exact
+
+
+def test_rows_beyond_the_batch_are_untouched(lin):
+    q4, L = lin
+    w, x = _case(9, 70, 256, 512)
+    geo = q4.bind_geometry(512, 256)
+    out = torch.full((128, 256), 7.0, dtype=torch.float32, device="cuda")
+    L.linear_f16(geo, torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda().half(), out=out[:70])
+    torch.cuda.synchronize()
+    assert bool((out[70:] == 7.0).all())
+    assert L.status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 4, 16, 200])
+def test_fp32_surface_like_the_reference_test(lin, M):
+    """q3_cuda_q4k_linear on the reference test's batch sizes and activation
+    pattern (tests/test_q3_q4_linear.cu:226-234, 294): finite, within the bars,
+    bit-exact on repetition, stats filled."""
+    q4, L = lin
+    N, K = 512, 2048
+    w, _ = _case(11, 1, N, K)
+    k = np.arange(K, dtype=np.float64)[None, :]
+    t = np.arange(M, dtype=np.float64)[:, None]
+    a = ((k * 17 + t * 131) % 1009) * 0.1
+    x = (0.5 * np.sin(a) + 0.25 * np.cos(a * 0.37)).astype(np.float32)
+    geo = q4.bind_geometry(K, N)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    from sera_c_b200._lib import LinearStats
+    st = LinearStats()
+    out = L.linear_f32(geo, wd, xd, stats=st)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    m = qo.linear_error_metrics(got, qo.q4k_linear(w, x))
+    assert m["cos"] > 0.99999 and m["rel_l2"] < 1e-3, m
+    out2 = L.linear_f32(geo, wd, xd)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    L.read_stats(st)
+    assert st.weight_bytes == N * (K // 256) * 144 and st.kernel_launches == 2
+    assert st.cuda_allocations == 0 and st.host_syncs == 0 and st.total_ms > 0
+    assert L.status() == 0
+
+
+def test_error_paths(lin):
+    q4, L = lin
+    from sera_c_b200 import Q3Error
+    geo = q4.bind_geometry(512, 256)
+    w = torch.zeros(256 * 2 * 144, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(8, 512, dtype=torch.float16, device="cuda")
+    with pytest.raises(Q3Error, match="Q6_K"):
+        L.linear_f16(q4.bind_geometry(512, 256, qtype=q4.Q6_K), w, x)
+    with pytest.raises(Q3Error, match="N of 128"):
+        L.linear_f16(q4.bind_geometry(512, 200), w, x)
+    with pytest.raises(Q3Error, match="workspace"):
+        big = torch.zeros(5000, 8192, dtype=torch.float32, device="cuda")
+        L.linear_f32(q4.bind_geometry(8192, 256), w, big)
+    with pytest.raises(Q3Error, match="multiple of 256"):
+        q4.bind_geometry(500, 256)
+    assert geo.weight_bytes == 256 * 2 * 144
+
+
+def test_against_reference_kernels(lin):
+    """The reference's own Q4_K linear (Q8_1 activation quantisation + MMVQ /
+    MMQ), compiled unchanged for sm_100a, on the same inputs: both must meet the
+    reference's bar against the exact oracle, and this library must be the closer."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libq3q4ref.so")
+    if not os.path.exists(path):
+        pytest.skip("reference Q4_K linear not built (make -C oracle refq4)")
+    q4, L = lin
+    from sera_c_b200 import _lib
+    R = _lib.bind_linear(ctypes.CDLL(path))
+    err = ctypes.create_string_buffer(512)
+    assert R.q3_cuda_q4k_linear_init(0, 512, 1024, 2048, err, 512), err.value
+    arena = torch.empty(max(int(R.q3_cuda_q4k_linear_workspace_bytes()), 256),
+                        dtype=torch.uint8, device="cuda")
+    assert R.q3_cuda_q4k_linear_set_workspace(arena.data_ptr(), arena.numel(), err, 512), err.value
+    N, K = 1024, 2048
+    for M in (1, 16, 64, 300):
+        w, x = _case(100 + M, M, N, K)
+        geo = q4.bind_geometry(K, N)
+        wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+        ref_out = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+        assert R.q3_cuda_q4k_linear(ctypes.byref(geo), wd.data_ptr(), xd.data_ptr(), M,
+                                    ref_out.data_ptr(), None, None, err, 512), err.value
+        torch.cuda.synchronize()
+        ours = L.linear_f32(geo, wd, xd)
+        torch.cuda.synchronize()
+        exact = qo.q4k_linear(w, x)
+        mr = qo.linear_error_metrics(ref_out.cpu().numpy(), exact)
+        mo = qo.linear_error_metrics(ours.cpu().numpy(), exact)
+        assert mr["cos"] > 0.999 and mr["rel_l2"] < 0.01, (M, mr)
+        assert mo["rel_l2"] < 1e-3 and mo["rel_l2"] < mr["rel_l2"], (M, mo, mr)

@@ -20,10 +20,12 @@ def pkg():
 
 def test_library_exports_every_declared_symbol(pkg):
     import ctypes
-    hdr = open(os.path.join(ROOT, "include", "q3_attn.h")).read()
-    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
-    names = set(re.findall(r"\b(q3_[a-z0-9_]+)\s*\(", hdr))
-    assert len(names) > 50
+    names = set()
+    for h in sorted(os.listdir(os.path.join(ROOT, "include"))):
+        hdr = open(os.path.join(ROOT, "include", h)).read()
+        hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+        names |= set(re.findall(r"\b(q3_[a-z0-9_]+)\s*\(", hdr))
+    assert len(names) > 60 and "q3_cuda_q4k_linear" in names
     L = ctypes.CDLL(pkg.lib_path())
     missing = [n for n in sorted(names) if not hasattr(L, n)]
     assert not missing, missing
