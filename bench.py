@@ -466,12 +466,67 @@ CASES = {
 }
 
 
+def random_q4k_weight(torch, n_features, k, device, seed=0):
+    """Synthetic resident Q4_K weight [n_features][k/256 blocks of 144 bytes]:
+    random scales, mins and quants; d, dmin (the two f16 at the head of each
+    block) drawn so that the weights are O(0.1)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    nb = n_features * (k // 256)
+    w = torch.randint(0, 256, (nb, 144), generator=g, device=device, dtype=torch.uint8)
+    d = (torch.rand(nb, generator=g, device=device) * 0.004 + 0.0004).to(torch.float16)
+    dmin = (torch.rand(nb, generator=g, device=device) * 0.002).to(torch.float16)
+    w[:, 0:2] = d.view(torch.uint8).view(nb, 2)
+    w[:, 2:4] = dmin.view(torch.uint8).view(nb, 2)
+    return w.view(n_features, -1)
+
+
+def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, reps=20):
+    """Resident Q4_K projection next to the attention path (q/k/v projection of
+    Qwen3-32B as one [10240, 5120] weight, or the output projection
+    [5120, 8192]): f16 activations in, bf16 out, one kernel. Six weight copies
+    are cycled so that every call reads its weight from HBM, not L2."""
+    from sera_c_b200 import q4_linear
+    peaks = measured_peaks()
+    lin = q4_linear.Q4Linear(device.index, M, N, K)
+    geo = q4_linear.bind_geometry(K, N)
+    copies = max(2, int(200e6 // geo.weight_bytes) + 1)
+    ws = [random_q4k_weight(torch, N, K, device, seed=i) for i in range(copies)]
+    g = torch.Generator(device=device).manual_seed(1)
+    x = torch.randn(M, K, generator=g, device=device).to(torch.float16)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+    for i in range(3):
+        lin.linear_f16(geo, ws[i % copies], x, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        lin.linear_f16(geo, ws[i % copies], x, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    flops = 2.0 * M * N * K
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"ms": ms, "tflops": tf, "frac_of_burst_peak": tf / peaks["tflops_burst"],
+            "tokens_per_s": M / (ms * 1e-3), "M": M, "N": N, "K": K,
+            "weight_bytes": int(geo.weight_bytes), "status": lin.status(),
+            "algorithmic_bytes": int(geo.weight_bytes + M * K * 2 + M * N * 2)}
+
+
+CASES.update({
+    "q4k_qkv_2048": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 2048, reps=reps),
+    "q4k_qkv_4096": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 4096, reps=reps),
+    "q4k_oproj_2048": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 2048, 5120, 8192, reps),
+    "q4k_qkv_16": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 16, reps=reps),
+})
+
+
 def run_extras(pkg, torch, device):
     """The other single-GPU configurations of the benchmark definition, one
     layer each: causal prefill (TFLOP/s), 8192-prefix cascade (tokens/s),
     paged decode (GB/s). Device-timed, inputs resident."""
     return {name: CASES[name](pkg, torch, device, 20)
-            for name in ("prefill_4096", "cascade_p8192_b64x24", "decode_256seq")}
+            for name in ("prefill_4096", "cascade_p8192_b64x24", "decode_256seq",
+                         "q4k_qkv_2048")}
 
 
 def run_case(args):
@@ -617,6 +672,29 @@ def reference_gpu_kernels():
     res["stack_layer_p32768_b128x16"] = cascade(PREFIX, BRANCHES, SUFFIX, 2)
     res["stack64_tokens_per_s_extrapolated"] = TOKENS / (
         res["stack_layer_p32768_b128x16"]["ms"] * 1e-3 * L)
+    # the reference's Q4_K linear (Q8_1 activation quantisation + MMQ) on the q/k/v shape
+    qpath = os.path.join(ROOT, "oracle", "_ref", "libq3q4ref.so")
+    if os.path.exists(qpath):
+        sys.path.insert(0, os.path.join(ROOT, "sera.c_b200"))
+        import __graft_entry__ as entry
+        entry.load_package()
+        from sera_c_b200 import _lib
+        Q = _lib.bind_linear(ctypes.CDLL(qpath))
+        M, N, K = 2048, (H + 2 * HKV) * D, 5120
+        geo = _lib.LinearGeometry()
+        ck(Q.q3_q4_linear_bind_geometry(12, K, N, ctypes.byref(geo), err, 256))
+        ck(Q.q3_cuda_q4k_linear_init(0, M, N, K, err, 256))
+        arena = torch.empty(max(int(Q.q3_cuda_q4k_linear_workspace_bytes()), 256),
+                            dtype=torch.uint8, device=dev)
+        ck(Q.q3_cuda_q4k_linear_set_workspace(arena.data_ptr(), arena.numel(), err, 256))
+        w = random_q4k_weight(torch, N, K, dev)
+        x = torch.randn(M, K, generator=g, dtype=f32, device=dev)
+        o = torch.zeros(M, N, dtype=f32, device=dev)
+        ms = timeit(lambda: ck(Q.q3_cuda_q4k_linear(ctypes.byref(geo), w.data_ptr(),
+                                                    x.data_ptr(), M, o.data_ptr(), None, None,
+                                                    err, 256)), 5)
+        res["q4k_qkv_2048"] = {"ms": ms, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12,
+                               "tokens_per_s": M / (ms * 1e-3)}
     res["note"] = ("reference SIMT kernels, fp32 contiguous KV, norm + rope + attention per "
                    "call, scatter of the suffix rows not timed (file-static in the reference)")
     return res

@@ -10,10 +10,10 @@
  *   warp 1      allocates tensor memory, issues tcgen05.mma (one thread)
  *   warp 2      TMA producer of the raw weight bytes: per 256 k one box of
  *               128 rows x 144 bytes (one Q4_K block per feature row)
- *   warps 4-11  dequantise: thread = (feature row, low/high nibble); per
- *               k-step 32 quants -> 32 f16 written straight into the swizzled
- *               K-major operand layout the MMA reads; afterwards the same
- *               warps drain the accumulators to global memory
+ *   warps 4..   dequantise, one group of 4 warps per operand stage: thread =
+ *               feature row; per k-step 64 quants -> 64 f16 written straight
+ *               into the swizzled K-major operand layout the MMA reads;
+ *               afterwards two of the groups drain the accumulators
  *
  * A k-step of 64 is exactly one 32-byte group of a block: its low nibbles are
  * elements 0..31, its high nibbles elements 32..63 (ref: src/q3_quant.c:57-76),
@@ -43,16 +43,19 @@ constexpr uint32_t kTileBytes = 128 * 64 * 2;      /* one 128 x 64 f16 operand t
 constexpr uint32_t kRawRowBytes = Q3_QUANT_Q4_K_BLOCK_BYTES;
 constexpr uint32_t kRawBytes = 128 * kRawRowBytes; /* 128 feature rows, one block each */
 constexpr uint32_t kRawStages = 2;
-constexpr uint32_t kThreads = 384;
-constexpr uint32_t kDequantThreads = 256;
-constexpr uint32_t kMaxStages = 4;
+constexpr uint32_t kMaxStages = 6;
 
 template <uint32_t MT>
 struct Layout {
-    static constexpr uint32_t kStages = MT == 1 ? 2u : 3u;
+    /* activation ring: deep enough to cover the TMA latency; weight-operand
+     * ring: one stage per dequantising warp group */
+    static constexpr uint32_t kXStages = MT == 1 ? 6u : 4u;
+    static constexpr uint32_t kBStages = 3u;
+    static constexpr uint32_t kDequantThreads = 128u * kBStages;
+    static constexpr uint32_t kThreads = 128u + kDequantThreads;
     static constexpr uint32_t kX = 0;
-    static constexpr uint32_t kB = kX + kStages * MT * kTileBytes;
-    static constexpr uint32_t kRaw = kB + kStages * kTileBytes;
+    static constexpr uint32_t kB = kX + kXStages * MT * kTileBytes;
+    static constexpr uint32_t kRaw = kB + kBStages * kTileBytes;
     static constexpr uint32_t kMisc = kRaw + kRawStages * kRawBytes;
     static constexpr uint32_t kTotal = kMisc + 256 + 1024; /* + alignment slack */
     static constexpr uint32_t kTmemCols = MT * 128;
@@ -60,7 +63,8 @@ struct Layout {
 
 struct Misc {
     uint64_t raw_full[kRawStages], raw_empty[kRawStages];
-    uint64_t x_full[kMaxStages], b_full[kMaxStages], kt_empty[kMaxStages];
+    uint64_t x_full[kMaxStages], x_empty[kMaxStages];
+    uint64_t b_full[kMaxStages], b_empty[kMaxStages];
     uint64_t acc_full;
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -83,20 +87,23 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, Mi
     return false;
 }
 
-/* Four bytes of 4-bit quants (already masked to 0x0F0F0F0F) -> four f16
- * weights q*scale - offset, in element order. 0x6400 | q is the f16 1024 + q. */
-__device__ __forceinline__ uint2 dequant4(uint32_t nib, __half2 scale, __half2 neg_offset) {
-    const __half2 k1024 = __half2half2(__ushort_as_half((unsigned short)0x6400));
-    uint32_t p01 = __byte_perm(nib, 0x64646464u, 0x4140);
-    uint32_t p23 = __byte_perm(nib, 0x64646464u, 0x4342);
-    __half2 h01 = __hsub2(*reinterpret_cast<__half2 *>(&p01), k1024);
-    __half2 h23 = __hsub2(*reinterpret_cast<__half2 *>(&p23), k1024);
-    h01 = __hfma2(h01, scale, neg_offset);
-    h23 = __hfma2(h23, scale, neg_offset);
-    uint2 r;
-    r.x = *reinterpret_cast<uint32_t *>(&h01);
-    r.y = *reinterpret_cast<uint32_t *>(&h23);
-    return r;
+/* `pair` holds two quant bytes in its 16-bit lanes (bits 0-7 of each lane).
+ * Low nibbles: 0x6400 | q is the f16 1024 + q. High nibbles: 0x5400 | (q << 4)
+ * is the f16 64 + q (one ulp there is 1/16). Subtracting the bias is exact;
+ * the result is f16(fma(q, scale, -offset)) for both lanes. */
+__device__ __forceinline__ uint32_t dequant_lo(uint32_t pair, __half2 scale,
+                                               __half2 neg_offset) {
+    uint32_t b = (pair & 0x000F000Fu) | 0x64006400u;
+    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6400));
+    __half2 h = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&b), bias), scale, neg_offset);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ uint32_t dequant_hi(uint32_t pair, __half2 scale,
+                                               __half2 neg_offset) {
+    uint32_t b = (pair & 0x00F000F0u) | 0x54005400u;
+    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x5400));
+    __half2 h = __hfma2(__hsub2(*reinterpret_cast<__half2 *>(&b), bias), scale, neg_offset);
+    return *reinterpret_cast<uint32_t *>(&h);
 }
 
 __device__ __forceinline__ void store_out32(const LinearParams &p, size_t off,
@@ -137,7 +144,7 @@ __device__ __forceinline__ void store_out32(const LinearParams &p, size_t off,
 }
 
 template <uint32_t MT>
-__global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1)
+__global__ void __launch_bounds__(Layout<MT>::kThreads, 1)
 q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                      const __grid_constant__ CUtensorMap w_map, const LinearParams p) {
     using L = Layout<MT>;
@@ -154,12 +161,15 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kRawStages; s++) {
             mbar_init(&misc->raw_full[s], 1);
-            mbar_init(&misc->raw_empty[s], kDequantThreads);
+            mbar_init(&misc->raw_empty[s], L::kDequantThreads);
         }
-        for (uint32_t s = 0; s < L::kStages; s++) {
+        for (uint32_t s = 0; s < L::kXStages; s++) {
             mbar_init(&misc->x_full[s], 1);
-            mbar_init(&misc->b_full[s], kDequantThreads);
-            mbar_init(&misc->kt_empty[s], 1);
+            mbar_init(&misc->x_empty[s], 1);
+        }
+        for (uint32_t s = 0; s < L::kBStages; s++) {
+            mbar_init(&misc->b_full[s], 128);
+            mbar_init(&misc->b_empty[s], 1);
         }
         mbar_init(&misc->acc_full, 1);
         misc->abort_flag = 0;
@@ -180,8 +190,8 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             prefetch_tmap(&x_map);
             bool alive = true;
             for (uint32_t kt = 0; kt < n_kt && alive; kt++) {
-                const uint32_t s = kt % L::kStages, use = kt / L::kStages;
-                if (use > 0) alive = wait_or_abort(&misc->kt_empty[s], (use - 1) & 1u, misc);
+                const uint32_t s = kt % L::kXStages, use = kt / L::kXStages;
+                if (use > 0) alive = wait_or_abort(&misc->x_empty[s], (use - 1) & 1u, misc);
                 if (!alive) break;
                 mbar_arrive_expect_tx(&misc->x_full[s], MT * kTileBytes);
 #pragma unroll
@@ -215,9 +225,9 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             const uint32_t b_addr = smem_u32(smem + L::kB);
             bool alive = true;
             for (uint32_t kt = 0; kt < n_kt; kt++) {
-                const uint32_t s = kt % L::kStages, use = kt / L::kStages;
-                alive = wait_or_abort(&misc->x_full[s], use & 1u, misc) &&
-                        wait_or_abort(&misc->b_full[s], use & 1u, misc);
+                const uint32_t s = kt % L::kXStages, bs = kt % L::kBStages;
+                alive = wait_or_abort(&misc->x_full[s], (kt / L::kXStages) & 1u, misc) &&
+                        wait_or_abort(&misc->b_full[bs], (kt / L::kBStages) & 1u, misc);
                 if (!alive) break;
                 tc_fence_after();
 #pragma unroll
@@ -226,89 +236,115 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                     for (uint32_t mt = 0; mt < MT; mt++)
                         umma_ss(tmem + mt * 128u,
                                 umma_desc(x_addr + (s * MT + mt) * kTileBytes + kk * 32u, 16, 1024),
-                                umma_desc(b_addr + s * kTileBytes + kk * 32u, 16, 1024), idesc,
+                                umma_desc(b_addr + bs * kTileBytes + kk * 32u, 16, 1024), idesc,
                                 (kt | kk) != 0u);
                 }
-                umma_commit(&misc->kt_empty[s]);
+                umma_commit(&misc->x_empty[s]);
+                umma_commit(&misc->b_empty[bs]);
             }
             if (alive) umma_commit(&misc->acc_full);
         }
         __syncwarp();
     } else if (warp >= 4) {
-        /* ============ dequantise, then drain the accumulators ============ */
-        const uint32_t d = threadIdx.x - 128u;
-        const uint32_t row = d & 127u;       /* feature row of the tile */
-        const uint32_t half = d >> 7;        /* 0: low nibbles, 1: high nibbles */
-        const uint32_t shift = half * 4u;
+        /* ============ dequantise, then drain the accumulators ============
+         * Group g (128 threads, one per feature row) owns operand stage g and
+         * converts k-steps g, g + kBStages, ...: the groups work on different
+         * k-steps at the same time, which hides the latency of one step's
+         * wait -> load -> convert -> store -> fence -> arrive chain. */
+        const uint32_t dq = threadIdx.x - 128u;
+        const uint32_t row = dq & 127u;
+        const uint32_t group = dq >> 7;
         const uint32_t swz = row & 7u;
+        uint8_t *brow = smem + L::kB + group * kTileBytes + row * 128u;
+        const uint8_t *blk = nullptr;
+        uint4 hdr = make_uint4(0, 0, 0, 0);
+        float dd = 0.f, dm = 0.f;
+        uint32_t cur_sb = 0xffffffffu;
         bool alive = true;
-        for (uint32_t sb = 0; sb < n_super && alive; sb++) {
-            const uint32_t rs = sb % kRawStages;
-            alive = wait_or_abort(&misc->raw_full[rs], (sb / kRawStages) & 1u, misc);
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) break;
-            const uint8_t *blk = smem + L::kRaw + rs * kRawBytes + row * kRawRowBytes;
-            const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-            const float dd = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
-            const float dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-#pragma unroll
-            for (uint32_t j = 0; j < 4; j++) {
-                /* sub-block 2j + half: scales bytes 0-3 = hdr.y, 4-7 = hdr.z, 8-11 = hdr.w */
-                const uint32_t bsh = ((2u * j + half) & 3u) * 8u;
-                uint32_t sc, mn;
-                if (j < 2) {
-                    sc = (hdr.y >> bsh) & 63u;
-                    mn = (hdr.z >> bsh) & 63u;
-                } else {
-                    const uint32_t hi = (hdr.w >> bsh) & 0xffu;
-                    sc = (hi & 0xFu) | ((((hdr.y >> bsh) & 0xffu) >> 6) << 4);
-                    mn = (hi >> 4) | ((((hdr.z >> bsh) & 0xffu) >> 6) << 4);
-                }
-                const __half2 scale = __float2half2_rn(dd * (float)sc);
-                const __half2 neg_offset = __hneg2(__float2half2_rn(dm * (float)mn));
-
-                const uint32_t kt = sb * 4u + j;
-                const uint32_t s = kt % L::kStages, use = kt / L::kStages;
-                if (use > 0) alive = wait_or_abort(&misc->kt_empty[s], (use - 1) & 1u, misc);
+        for (uint32_t kt = group, use = 0; kt < n_kt; kt += L::kBStages, use++) {
+            const uint32_t sb = kt >> 2, j = kt & 3u;
+            if (sb != cur_sb) {
+                if (cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
+                const uint32_t rs = sb % kRawStages;
+                alive = wait_or_abort(&misc->raw_full[rs], (sb / kRawStages) & 1u, misc);
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
-                const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16u + 32u * j);
-                const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32u + 32u * j);
-                uint8_t *brow = smem + L::kB + s * kTileBytes + row * 128u;
-                const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-                for (uint32_t c = 0; c < 4; c++) {
-                    /* 8 quant bytes -> 8 f16 = one 16-byte chunk of the operand row */
-                    const uint2 lo = dequant4((w[2 * c] >> shift) & 0x0F0F0F0Fu, scale, neg_offset);
-                    const uint2 hi = dequant4((w[2 * c + 1] >> shift) & 0x0F0F0F0Fu, scale,
-                                              neg_offset);
-                    const uint32_t chunk = (half * 4u + c) ^ swz;
-                    *reinterpret_cast<uint4 *>(brow + chunk * 16u) =
-                        make_uint4(lo.x, lo.y, hi.x, hi.y);
-                }
-                fence_proxy_async();
-                mbar_arrive(&misc->b_full[s]);
+                cur_sb = sb;
+                blk = smem + L::kRaw + rs * kRawBytes + row * kRawRowBytes;
+                hdr = *reinterpret_cast<const uint4 *>(blk);
+                dd = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+                dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
             }
-            if (alive) mbar_arrive(&misc->raw_empty[rs]);
-        }
+            /* sub-blocks 2j (low nibbles) and 2j+1 (high nibbles); scales bytes
+             * 0-3 = hdr.y, 4-7 = hdr.z, 8-11 = hdr.w */
+            const uint32_t bsh = (j & 1u) * 16u;
+            uint32_t sc_lo, mn_lo, sc_hi, mn_hi;
+            if (j < 2) {
+                const uint32_t a = hdr.y >> bsh, b = hdr.z >> bsh;
+                sc_lo = a & 63u;
+                mn_lo = b & 63u;
+                sc_hi = (a >> 8) & 63u;
+                mn_hi = (b >> 8) & 63u;
+            } else {
+                const uint32_t a = hdr.y >> bsh, b = hdr.z >> bsh, c = hdr.w >> bsh;
+                sc_lo = (c & 0xFu) | (((a & 0xffu) >> 6) << 4);
+                mn_lo = ((c & 0xffu) >> 4) | (((b & 0xffu) >> 6) << 4);
+                sc_hi = ((c >> 8) & 0xFu) | ((((a >> 8) & 0xffu) >> 6) << 4);
+                mn_hi = (((c >> 8) & 0xffu) >> 4) | ((((b >> 8) & 0xffu) >> 6) << 4);
+            }
+            const __half2 scale_lo = __float2half2_rn(dd * (float)sc_lo);
+            const __half2 scale_hi = __float2half2_rn(dd * (float)sc_hi);
+            const __half2 noff_lo = __hneg2(__float2half2_rn(dm * (float)mn_lo));
+            const __half2 noff_hi = __hneg2(__float2half2_rn(dm * (float)mn_hi));
 
-        if (alive) alive = wait_or_abort(&misc->acc_full, 0u, misc);
-        alive = __all_sync(0xffffffffu, alive);
-        if (alive) {
-            tc_fence_after();
-            const uint32_t quarter = warp & 3u;          /* tensor-memory lanes 32*quarter.. */
-            const uint32_t group = (warp - 4u) >> 2;     /* 0 or 1 */
-            const uint32_t mt = MT == 2 ? group : 0u;
-            const uint32_t col0 = MT == 2 ? 0u : group * 64u;
-            const uint32_t n_chunks = MT == 2 ? 4u : 2u;
-            const uint32_t token = m0 + mt * 128u + quarter * 32u + lane;
-            const uint32_t taddr = tmem + ((quarter * 32u) << 16) + mt * 128u + col0;
-            for (uint32_t ch = 0; ch < n_chunks; ch++) {
-                uint32_t v[32];
-                tmem_ld32(taddr + ch * 32u, v);
-                tmem_wait_ld();
-                if (token < p.M)
-                    store_out32(p, (size_t)token * p.N + n0 + col0 + ch * 32u, v);
+            if (use > 0) alive = wait_or_abort(&misc->b_empty[group], (use - 1) & 1u, misc);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16u + 32u * j);
+            const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32u + 32u * j);
+            const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+            for (uint32_t c = 0; c < 4; c++) {
+                /* quant bytes 8c..8c+7: low nibbles -> elements 8c.., chunk c;
+                 * high nibbles -> elements 32+8c.., chunk 4+c */
+                uint32_t lo[4], hi[4];
+#pragma unroll
+                for (uint32_t u = 0; u < 2; u++) {
+                    const uint32_t p01 = __byte_perm(w[2 * c + u], 0u, 0x4140);
+                    const uint32_t p23 = __byte_perm(w[2 * c + u], 0u, 0x4342);
+                    lo[2 * u] = dequant_lo(p01, scale_lo, noff_lo);
+                    lo[2 * u + 1] = dequant_lo(p23, scale_lo, noff_lo);
+                    hi[2 * u] = dequant_hi(p01, scale_hi, noff_hi);
+                    hi[2 * u + 1] = dequant_hi(p23, scale_hi, noff_hi);
+                }
+                *reinterpret_cast<uint4 *>(brow + ((c ^ swz) * 16u)) =
+                    make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4 *>(brow + (((4u + c) ^ swz) * 16u)) =
+                    make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            }
+            fence_proxy_async();
+            mbar_arrive(&misc->b_full[group]);
+        }
+        if (alive && cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
+
+        if (group < 2) {
+            if (alive) alive = wait_or_abort(&misc->acc_full, 0u, misc);
+            alive = __all_sync(0xffffffffu, alive);
+            if (alive) {
+                tc_fence_after();
+                const uint32_t quarter = warp & 3u;      /* tensor-memory lanes 32*quarter.. */
+                const uint32_t mt = MT == 2 ? group : 0u;
+                const uint32_t col0 = MT == 2 ? 0u : group * 64u;
+                const uint32_t n_chunks = MT == 2 ? 4u : 2u;
+                const uint32_t token = m0 + mt * 128u + quarter * 32u + lane;
+                const uint32_t taddr = tmem + ((quarter * 32u) << 16) + mt * 128u + col0;
+                for (uint32_t ch = 0; ch < n_chunks; ch++) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32u, v);
+                    tmem_wait_ld();
+                    if (token < p.M)
+                        store_out32(p, (size_t)token * p.N + n0 + col0 + ch * 32u, v);
+                }
             }
         }
     }
@@ -353,15 +389,16 @@ size_t arena_bytes(size_t max_tokens, int64_t max_k) {
     return (b + 255) & ~(size_t)255;
 }
 
-/* MT = 2 (256 tokens per CTA, one CTA per SM) halves the dequantisation work
- * per FLOP; MT = 1 (two CTAs per SM) wins when it needs fewer waves. */
+/* MT = 2 (256 tokens per CTA) halves the dequantisation work and the weight
+ * operand traffic per FLOP; MT = 1 is for batches of at most 128 tokens or
+ * when it needs less time (waves of 128-token tiles cost half as much). */
 uint32_t choose_mt(uint32_t M, uint32_t N, int sm_count) {
     if (M <= 128) return 1;
     const uint64_t t1 = (uint64_t)((M + 127) / 128) * (N / 128);
     const uint64_t t2 = (uint64_t)((M + 255) / 256) * (N / 128);
-    const uint64_t w1 = (t1 + 2ull * sm_count - 1) / (2ull * sm_count);
-    const uint64_t w2 = (t2 + sm_count - 1) / sm_count;
-    return w2 <= w1 ? 2 : 1;
+    const uint64_t w1 = (t1 + sm_count - 1) / sm_count;        /* waves of cost 1 */
+    const uint64_t w2 = 2 * ((t2 + sm_count - 1) / sm_count);  /* waves of cost 2 */
+    return w2 <= w1 + w1 / 8 ? 2 : 1;
 }
 
 bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const void *x_f16,
@@ -392,10 +429,10 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g.device);
     if (choose_mt(M, N, sms) == 2) {
         dim3 grid((M + 255) / 256, N / 128);
-        q4k_linear_tc_kernel<2><<<grid, kThreads, Layout<2>::kTotal, stream>>>(x_map, w_map, p);
+        q4k_linear_tc_kernel<2><<<grid, Layout<2>::kThreads, Layout<2>::kTotal, stream>>>(x_map, w_map, p);
     } else {
         dim3 grid((M + 127) / 128, N / 128);
-        q4k_linear_tc_kernel<1><<<grid, kThreads, Layout<1>::kTotal, stream>>>(x_map, w_map, p);
+        q4k_linear_tc_kernel<1><<<grid, Layout<1>::kThreads, Layout<1>::kTotal, stream>>>(x_map, w_map, p);
     }
     Q3_LAUNCH_CHECK("q4k_linear_tc launch failed");
     return true;

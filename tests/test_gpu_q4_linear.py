@@ -120,8 +120,11 @@ def test_error_paths(lin):
 
 def test_against_reference_kernels(lin):
     """The reference's own Q4_K linear (Q8_1 activation quantisation + MMVQ /
-    MMQ), compiled unchanged for sm_100a, on the same inputs: both must meet the
-    reference's bar against the exact oracle, and this library must be the closer."""
+    MMQ), compiled unchanged for sm_100a, on the same inputs: this library must
+    be the closer to the exact oracle. On these synthetic inputs (uniformly
+    random quants, N(0,1) activations) the reference's Q8_1 activation
+    quantisation alone costs about 1 % relative L2 error, so its own bar
+    (1 %, stated for model weights) is widened to 3 % for it here."""
     path = os.path.join(ROOT, "oracle", "_ref", "libq3q4ref.so")
     if not os.path.exists(path):
         pytest.skip("reference Q4_K linear not built (make -C oracle refq4)")
@@ -147,5 +150,5 @@ def test_against_reference_kernels(lin):
         exact = qo.q4k_linear(w, x)
         mr = qo.linear_error_metrics(ref_out.cpu().numpy(), exact)
         mo = qo.linear_error_metrics(ours.cpu().numpy(), exact)
-        assert mr["cos"] > 0.999 and mr["rel_l2"] < 0.01, (M, mr)
+        assert mr["cos"] > 0.999 and mr["rel_l2"] < 0.03, (M, mr)
         assert mo["rel_l2"] < 1e-3 and mo["rel_l2"] < mr["rel_l2"], (M, mo, mr)
