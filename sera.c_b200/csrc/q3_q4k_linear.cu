@@ -1,19 +1,26 @@
 /* q3_q4k_linear.cu - resident Q4_K weight x activation on the sm_100a tensor
- * cores (tcgen05, accumulators in tensor memory).
+ * cores (tcgen05, accumulators and the weight operand in tensor memory).
  *
  *   out[token][feature] = sum_k W[feature][k] * x[token][k]
  *
  * W stays in its 144-byte Q4_K blocks in HBM (ref: src/q3_quant.h:24-33). A CTA
- * owns a tile of MT*128 tokens x 128 features and walks K in steps of 64:
+ * owns 128 features x NT tokens (NT <= 256) and walks K in steps of 64. The MMA
+ * runs transposed: D[feature][token] += W[feature][k] * x[token][k], M = 128
+ * features (tensor-memory lanes), N = NT tokens, with
+ *   A = W tile, dequantised to f16 by the CTA's warps and stored straight
+ *       into tensor memory (tcgen05.st; thread = feature row = lane), and
+ *   B = x tile [NT tokens][64 k] f16 in shared memory (TMA, 128-byte swizzle).
+ * Keeping the weight operand out of shared memory matters: with both operands
+ * in shared memory this kernel was bound by shared-memory bandwidth (operand
+ * stores + TMA writes + MMA reads were about 240 B/clk at full tensor rate).
  *
- *   warp 0      TMA producer of the activation tiles (f16, 128-byte swizzle)
+ *   warp 0      TMA producer of the activation tiles
  *   warp 1      allocates tensor memory, issues tcgen05.mma (one thread)
  *   warp 2      TMA producer of the raw weight bytes: per 256 k one box of
  *               128 rows x 144 bytes (one Q4_K block per feature row)
- *   warps 4..   dequantise, one group of 4 warps per operand stage: thread =
- *               feature row; per k-step 64 quants -> 64 f16 written straight
- *               into the swizzled K-major operand layout the MMA reads;
- *               afterwards two of the groups drain the accumulators
+ *   warps 4-15  three groups of four warps dequantise: group g takes k-steps
+ *               g, g+3, ...; thread = feature row; 64 quants -> 32 packed f16
+ *               registers -> tcgen05.st; afterwards all of them drain D
  *
  * A k-step of 64 is exactly one 32-byte group of a block: its low nibbles are
  * elements 0..31, its high nibbles elements 32..63 (ref: src/q3_quant.c:57-76),
@@ -39,32 +46,29 @@
 namespace {
 using namespace q3ptx;
 
-constexpr uint32_t kTileBytes = 128 * 64 * 2;      /* one 128 x 64 f16 operand tile */
 constexpr uint32_t kRawRowBytes = Q3_QUANT_Q4_K_BLOCK_BYTES;
 constexpr uint32_t kRawBytes = 128 * kRawRowBytes; /* 128 feature rows, one block each */
 constexpr uint32_t kRawStages = 2;
-constexpr uint32_t kMaxStages = 6;
-
-template <uint32_t MT>
-struct Layout {
-    /* activation ring: deep enough to cover the TMA latency; weight-operand
-     * ring: one stage per dequantising warp group */
-    static constexpr uint32_t kXStages = MT == 1 ? 6u : 4u;
-    static constexpr uint32_t kBStages = 3u;
-    static constexpr uint32_t kDequantThreads = 128u * kBStages;
-    static constexpr uint32_t kThreads = 128u + kDequantThreads;
-    static constexpr uint32_t kX = 0;
-    static constexpr uint32_t kB = kX + kXStages * MT * kTileBytes;
-    static constexpr uint32_t kRaw = kB + kBStages * kTileBytes;
-    static constexpr uint32_t kMisc = kRaw + kRawStages * kRawBytes;
-    static constexpr uint32_t kTotal = kMisc + 256 + 1024; /* + alignment slack */
-    static constexpr uint32_t kTmemCols = MT * 128;
-};
+constexpr uint32_t kMaxTokens = 256;               /* token tile = MMA N */
+constexpr uint32_t kXStageBytes = kMaxTokens * 128; /* [256 tokens][64 k] f16 */
+constexpr uint32_t kXStages = 5;
+constexpr uint32_t kAStages = 6;                   /* weight operand stages in tensor memory */
+constexpr uint32_t kGroups = 3;                    /* dequantising warp groups */
+constexpr uint32_t kThreads = 128 + 128 * kGroups;
+constexpr uint32_t kColD = 0;                      /* D: 128 lanes x 256 fp32 columns */
+constexpr uint32_t kColA = 256;                    /* A stage: 128 lanes x 32 columns (64 f16) */
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSmemX = 0;
+constexpr uint32_t kSmemRaw = kSmemX + kXStages * kXStageBytes;
+constexpr uint32_t kSmemMisc = kSmemRaw + kRawStages * kRawBytes;
+constexpr uint32_t kSmemTotal = kSmemMisc + 256 + 1024; /* + alignment slack */
+static_assert(kColA + kAStages * 32 <= kTmemCols, "tensor memory budget");
+static_assert(kAStages % kGroups == 0, "a group must come back to its own stages");
 
 struct Misc {
     uint64_t raw_full[kRawStages], raw_empty[kRawStages];
-    uint64_t x_full[kMaxStages], x_empty[kMaxStages];
-    uint64_t b_full[kMaxStages], b_empty[kMaxStages];
+    uint64_t x_full[kXStages], x_empty[kXStages];
+    uint64_t a_full[kAStages], a_empty[kAStages];
     uint64_t acc_full;
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -74,6 +78,7 @@ static_assert(sizeof(Misc) <= 256, "Misc must fit its slot");
 struct LinearParams {
     void *out;
     uint32_t M, N, K;
+    uint32_t NT;          /* tokens per CTA: multiple of 16, <= 256 */
     uint32_t out_type;
     uint32_t *status;
 };
@@ -106,54 +111,15 @@ __device__ __forceinline__ uint32_t dequant_hi(uint32_t pair, __half2 scale,
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
-__device__ __forceinline__ void store_out32(const LinearParams &p, size_t off,
-                                            const uint32_t *v) {
-    const float *f = reinterpret_cast<const float *>(v);
-    if (p.out_type == Q3_OUT_F32) {
-        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + off);
-#pragma unroll
-        for (uint32_t i = 0; i < 8; i++)
-            dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-    } else if (p.out_type == Q3_OUT_BF16) {
-        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.out) + off);
-#pragma unroll
-        for (uint32_t i = 0; i < 4; i++) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(f[8 * i], f[8 * i + 1]);
-            __nv_bfloat162 b = __floats2bfloat162_rn(f[8 * i + 2], f[8 * i + 3]);
-            __nv_bfloat162 c = __floats2bfloat162_rn(f[8 * i + 4], f[8 * i + 5]);
-            __nv_bfloat162 d = __floats2bfloat162_rn(f[8 * i + 6], f[8 * i + 7]);
-            dst[i] = make_uint4(*reinterpret_cast<uint32_t *>(&a),
-                                *reinterpret_cast<uint32_t *>(&b),
-                                *reinterpret_cast<uint32_t *>(&c),
-                                *reinterpret_cast<uint32_t *>(&d));
-        }
-    } else {
-        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__half *>(p.out) + off);
-#pragma unroll
-        for (uint32_t i = 0; i < 4; i++) {
-            __half2 a = __floats2half2_rn(f[8 * i], f[8 * i + 1]);
-            __half2 b = __floats2half2_rn(f[8 * i + 2], f[8 * i + 3]);
-            __half2 c = __floats2half2_rn(f[8 * i + 4], f[8 * i + 5]);
-            __half2 d = __floats2half2_rn(f[8 * i + 6], f[8 * i + 7]);
-            dst[i] = make_uint4(*reinterpret_cast<uint32_t *>(&a),
-                                *reinterpret_cast<uint32_t *>(&b),
-                                *reinterpret_cast<uint32_t *>(&c),
-                                *reinterpret_cast<uint32_t *>(&d));
-        }
-    }
-}
-
-template <uint32_t MT>
-__global__ void __launch_bounds__(Layout<MT>::kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                      const __grid_constant__ CUtensorMap w_map, const LinearParams p) {
-    using L = Layout<MT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    Misc *misc = reinterpret_cast<Misc *>(smem + L::kMisc);
+    Misc *misc = reinterpret_cast<Misc *>(smem + kSmemMisc);
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t m0 = blockIdx.x * (MT * 128u);
+    const uint32_t m0 = blockIdx.x * p.NT;
     const uint32_t n0 = blockIdx.y * 128u;
     const uint32_t n_super = p.K / Q3_QUANT_QK_K;   /* Q4_K blocks per feature row */
     const uint32_t n_kt = n_super * 4u;             /* k-steps of 64 */
@@ -161,22 +127,22 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kRawStages; s++) {
             mbar_init(&misc->raw_full[s], 1);
-            mbar_init(&misc->raw_empty[s], L::kDequantThreads);
+            mbar_init(&misc->raw_empty[s], 128 * kGroups);
         }
-        for (uint32_t s = 0; s < L::kXStages; s++) {
+        for (uint32_t s = 0; s < kXStages; s++) {
             mbar_init(&misc->x_full[s], 1);
             mbar_init(&misc->x_empty[s], 1);
         }
-        for (uint32_t s = 0; s < L::kBStages; s++) {
-            mbar_init(&misc->b_full[s], 128);
-            mbar_init(&misc->b_empty[s], 1);
+        for (uint32_t s = 0; s < kAStages; s++) {
+            mbar_init(&misc->a_full[s], 128);
+            mbar_init(&misc->a_empty[s], 1);
         }
         mbar_init(&misc->acc_full, 1);
         misc->abort_flag = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc(&misc->tmem_base, L::kTmemCols);
+        tmem_alloc(&misc->tmem_base, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -190,15 +156,12 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             prefetch_tmap(&x_map);
             bool alive = true;
             for (uint32_t kt = 0; kt < n_kt && alive; kt++) {
-                const uint32_t s = kt % L::kXStages, use = kt / L::kXStages;
+                const uint32_t s = kt % kXStages, use = kt / kXStages;
                 if (use > 0) alive = wait_or_abort(&misc->x_empty[s], (use - 1) & 1u, misc);
                 if (!alive) break;
-                mbar_arrive_expect_tx(&misc->x_full[s], MT * kTileBytes);
-#pragma unroll
-                for (uint32_t mt = 0; mt < MT; mt++)
-                    tma_load_2d(smem + L::kX + (s * MT + mt) * kTileBytes, &x_map,
-                                (int32_t)(kt * 64u), (int32_t)(m0 + mt * 128u),
-                                &misc->x_full[s]);
+                mbar_arrive_expect_tx(&misc->x_full[s], p.NT * 128u);
+                tma_load_2d(smem + kSmemX + s * kXStageBytes, &x_map, (int32_t)(kt * 64u),
+                            (int32_t)m0, &misc->x_full[s]);
             }
         }
         __syncwarp();
@@ -212,7 +175,7 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                 if (use > 0) alive = wait_or_abort(&misc->raw_empty[rs], (use - 1) & 1u, misc);
                 if (!alive) break;
                 mbar_arrive_expect_tx(&misc->raw_full[rs], kRawBytes);
-                tma_load_2d(smem + L::kRaw + rs * kRawBytes, &w_map,
+                tma_load_2d(smem + kSmemRaw + rs * kRawBytes, &w_map,
                             (int32_t)(sb * kRawRowBytes), (int32_t)n0, &misc->raw_full[rs]);
             }
         }
@@ -220,48 +183,41 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
     } else if (warp == 1) {
         /* ============ MMA issuer ============ */
         if (elect_one()) {
-            constexpr uint32_t idesc = umma_idesc_f16(128, 128, false);
-            const uint32_t x_addr = smem_u32(smem + L::kX);
-            const uint32_t b_addr = smem_u32(smem + L::kB);
+            const uint32_t idesc = umma_idesc_f16(128, p.NT, false);
+            const uint32_t x_addr = smem_u32(smem + kSmemX);
             bool alive = true;
             for (uint32_t kt = 0; kt < n_kt; kt++) {
-                const uint32_t s = kt % L::kXStages, bs = kt % L::kBStages;
-                alive = wait_or_abort(&misc->x_full[s], (kt / L::kXStages) & 1u, misc) &&
-                        wait_or_abort(&misc->b_full[bs], (kt / L::kBStages) & 1u, misc);
+                const uint32_t sx = kt % kXStages, sa = kt % kAStages;
+                alive = wait_or_abort(&misc->x_full[sx], (kt / kXStages) & 1u, misc) &&
+                        wait_or_abort(&misc->a_full[sa], (kt / kAStages) & 1u, misc);
                 if (!alive) break;
                 tc_fence_after();
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; kk++) {
-#pragma unroll
-                    for (uint32_t mt = 0; mt < MT; mt++)
-                        umma_ss(tmem + mt * 128u,
-                                umma_desc(x_addr + (s * MT + mt) * kTileBytes + kk * 32u, 16, 1024),
-                                umma_desc(b_addr + bs * kTileBytes + kk * 32u, 16, 1024), idesc,
-                                (kt | kk) != 0u);
-                }
-                umma_commit(&misc->x_empty[s]);
-                umma_commit(&misc->b_empty[bs]);
+                for (uint32_t kk = 0; kk < 4; kk++)
+                    umma_ts(tmem + kColD, tmem + kColA + sa * 32u + kk * 8u,
+                            umma_desc(x_addr + sx * kXStageBytes + kk * 32u, 16, 1024), idesc,
+                            (kt | kk) != 0u);
+                umma_commit(&misc->x_empty[sx]);
+                umma_commit(&misc->a_empty[sa]);
             }
             if (alive) umma_commit(&misc->acc_full);
         }
         __syncwarp();
     } else if (warp >= 4) {
-        /* ============ dequantise, then drain the accumulators ============
-         * Group g (128 threads, one per feature row) owns operand stage g and
-         * converts k-steps g, g + kBStages, ...: the groups work on different
-         * k-steps at the same time, which hides the latency of one step's
-         * wait -> load -> convert -> store -> fence -> arrive chain. */
+        /* ============ dequantise into tensor memory, then drain D ============
+         * Group g (128 threads, one per feature row) converts k-steps g, g+3,
+         * ...: the groups work on different k-steps at the same time, which
+         * hides the latency of one step's wait -> load -> convert -> store. */
         const uint32_t dq = threadIdx.x - 128u;
-        const uint32_t row = dq & 127u;
+        const uint32_t row = dq & 127u;              /* feature row = tensor-memory lane */
         const uint32_t group = dq >> 7;
-        const uint32_t swz = row & 7u;
-        uint8_t *brow = smem + L::kB + group * kTileBytes + row * 128u;
+        const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
         const uint8_t *blk = nullptr;
         uint4 hdr = make_uint4(0, 0, 0, 0);
         float dd = 0.f, dm = 0.f;
         uint32_t cur_sb = 0xffffffffu;
         bool alive = true;
-        for (uint32_t kt = group, use = 0; kt < n_kt; kt += L::kBStages, use++) {
+        for (uint32_t kt = group; kt < n_kt; kt += kGroups) {
             const uint32_t sb = kt >> 2, j = kt & 3u;
             if (sb != cur_sb) {
                 if (cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
@@ -270,7 +226,7 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 cur_sb = sb;
-                blk = smem + L::kRaw + rs * kRawBytes + row * kRawRowBytes;
+                blk = smem + kSmemRaw + rs * kRawBytes + row * kRawRowBytes;
                 hdr = *reinterpret_cast<const uint4 *>(blk);
                 dd = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
                 dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
@@ -297,53 +253,59 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             const __half2 noff_lo = __hneg2(__float2half2_rn(dm * (float)mn_lo));
             const __half2 noff_hi = __hneg2(__float2half2_rn(dm * (float)mn_hi));
 
-            if (use > 0) alive = wait_or_abort(&misc->b_empty[group], (use - 1) & 1u, misc);
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) break;
             const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16u + 32u * j);
             const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32u + 32u * j);
             const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            /* register i = elements (2i, 2i+1) of the k-step: low nibbles of the
+             * 32 quant bytes are elements 0..31, high nibbles elements 32..63 */
+            uint32_t v[32];
 #pragma unroll
-            for (uint32_t c = 0; c < 4; c++) {
-                /* quant bytes 8c..8c+7: low nibbles -> elements 8c.., chunk c;
-                 * high nibbles -> elements 32+8c.., chunk 4+c */
-                uint32_t lo[4], hi[4];
-#pragma unroll
-                for (uint32_t u = 0; u < 2; u++) {
-                    const uint32_t p01 = __byte_perm(w[2 * c + u], 0u, 0x4140);
-                    const uint32_t p23 = __byte_perm(w[2 * c + u], 0u, 0x4342);
-                    lo[2 * u] = dequant_lo(p01, scale_lo, noff_lo);
-                    lo[2 * u + 1] = dequant_lo(p23, scale_lo, noff_lo);
-                    hi[2 * u] = dequant_hi(p01, scale_hi, noff_hi);
-                    hi[2 * u + 1] = dequant_hi(p23, scale_hi, noff_hi);
-                }
-                *reinterpret_cast<uint4 *>(brow + ((c ^ swz) * 16u)) =
-                    make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                *reinterpret_cast<uint4 *>(brow + (((4u + c) ^ swz) * 16u)) =
-                    make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            for (uint32_t u = 0; u < 8; u++) {
+                const uint32_t p01 = __byte_perm(w[u], 0u, 0x4140);
+                const uint32_t p23 = __byte_perm(w[u], 0u, 0x4342);
+                v[2 * u] = dequant_lo(p01, scale_lo, noff_lo);
+                v[2 * u + 1] = dequant_lo(p23, scale_lo, noff_lo);
+                v[16 + 2 * u] = dequant_hi(p01, scale_hi, noff_hi);
+                v[16 + 2 * u + 1] = dequant_hi(p23, scale_hi, noff_hi);
             }
-            fence_proxy_async();
-            mbar_arrive(&misc->b_full[group]);
+            const uint32_t sa = kt % kAStages, use = kt / kAStages;
+            if (use > 0) alive = wait_or_abort(&misc->a_empty[sa], (use - 1) & 1u, misc);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) break;
+            tc_fence_after();
+            tmem_st32(tmem + lane_base + kColA + sa * 32u, v);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&misc->a_full[sa]);
         }
         if (alive && cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
 
-        if (group < 2) {
-            if (alive) alive = wait_or_abort(&misc->acc_full, 0u, misc);
-            alive = __all_sync(0xffffffffu, alive);
-            if (alive) {
-                tc_fence_after();
-                const uint32_t quarter = warp & 3u;      /* tensor-memory lanes 32*quarter.. */
-                const uint32_t mt = MT == 2 ? group : 0u;
-                const uint32_t col0 = MT == 2 ? 0u : group * 64u;
-                const uint32_t n_chunks = MT == 2 ? 4u : 2u;
-                const uint32_t token = m0 + mt * 128u + quarter * 32u + lane;
-                const uint32_t taddr = tmem + ((quarter * 32u) << 16) + mt * 128u + col0;
-                for (uint32_t ch = 0; ch < n_chunks; ch++) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + ch * 32u, v);
-                    tmem_wait_ld();
-                    if (token < p.M)
-                        store_out32(p, (size_t)token * p.N + n0 + col0 + ch * 32u, v);
+        if (alive) alive = wait_or_abort(&misc->acc_full, 0u, misc);
+        alive = __all_sync(0xffffffffu, alive);
+        if (alive) {
+            tc_fence_after();
+            /* lane = feature, column = token: the 32 lanes of a warp store 32
+             * consecutive features of one token per instruction */
+            const uint32_t feature = n0 + row;
+            const uint32_t n_chunks = (p.NT + 31u) / 32u;
+            for (uint32_t ch = group; ch < n_chunks; ch += kGroups) {
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + kColD + ch * 32u, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (uint32_t i = 0; i < 32; i++) {
+                    const uint32_t t = ch * 32u + i;
+                    const uint32_t token = m0 + t;
+                    if (t < p.NT && token < p.M) {
+                        const size_t off = (size_t)token * p.N + feature;
+                        const float f = __uint_as_float(v[i]);
+                        if (p.out_type == Q3_OUT_F32)
+                            static_cast<float *>(p.out)[off] = f;
+                        else if (p.out_type == Q3_OUT_BF16)
+                            static_cast<__nv_bfloat16 *>(p.out)[off] = __float2bfloat16_rn(f);
+                        else
+                            static_cast<__half *>(p.out)[off] = __float2half_rn(f);
+                    }
                 }
             }
         }
@@ -352,7 +314,7 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && misc->abort_flag) atomicOr(p.status, 1u);
-    if (warp == 1) tmem_dealloc(tmem, L::kTmemCols);
+    if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
 /* fp32 -> f16, 8 elements per thread (n is a multiple of 256: K is). */
@@ -389,16 +351,24 @@ size_t arena_bytes(size_t max_tokens, int64_t max_k) {
     return (b + 255) & ~(size_t)255;
 }
 
-/* MT = 2 (256 tokens per CTA) halves the dequantisation work and the weight
- * operand traffic per FLOP; MT = 1 is for batches of at most 128 tokens or
- * when it needs less time (waves of 128-token tiles cost half as much). */
-uint32_t choose_mt(uint32_t M, uint32_t N, int sm_count) {
-    if (M <= 128) return 1;
-    const uint64_t t1 = (uint64_t)((M + 127) / 128) * (N / 128);
-    const uint64_t t2 = (uint64_t)((M + 255) / 256) * (N / 128);
-    const uint64_t w1 = (t1 + sm_count - 1) / sm_count;        /* waves of cost 1 */
-    const uint64_t w2 = 2 * ((t2 + sm_count - 1) / sm_count);  /* waves of cost 2 */
-    return w2 <= w1 + w1 / 8 ? 2 : 1;
+/* Tokens per CTA (the MMA N, any multiple of 16 up to 256): the whole batch
+ * when it fits one tile; otherwise the size that minimises
+ * waves x (NT + 32) - a wave lasts as long as its token tile, and the +32
+ * stands for the per-tile work that does not shrink with NT (dequantisation,
+ * pipeline fill, drain). */
+uint32_t choose_token_tile(uint32_t M, uint32_t N, int sm_count) {
+    if (M <= kMaxTokens) return (M + 15u) & ~15u;
+    uint32_t best = kMaxTokens;
+    uint64_t best_cost = ~0ull;
+    for (uint32_t nt = kMaxTokens; nt >= 96; nt -= 16) {
+        const uint64_t tiles = (uint64_t)((M + nt - 1) / nt) * (N / 128);
+        const uint64_t cost = ((tiles + sm_count - 1) / sm_count) * (nt + 32ull);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = nt;
+        }
+    }
+    return best;
 }
 
 bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const void *x_f16,
@@ -413,27 +383,23 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
                        "q3_q4_linear: K must be a multiple of 256 and N of 128");
     if (((uintptr_t)weight | (uintptr_t)x_f16 | (uintptr_t)out) & 15u)
         return q3_fail(error, error_len, "q3_q4_linear: pointers must be 16-byte aligned");
-    CUtensorMap x_map, w_map;
-    if (!q3_encode_tmap_2d(&x_map, x_f16, K, M, 64, 128, error, error_len)) return false;
-    if (!q3_encode_tmap_bytes_2d(&w_map, weight, (uint64_t)(K / Q3_QUANT_QK_K) * kRawRowBytes,
-                                 N, kRawRowBytes, 128, error, error_len))
-        return false;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g.device);
     LinearParams p;
     p.out = out;
     p.M = M;
     p.N = N;
     p.K = K;
+    p.NT = choose_token_tile(M, N, sms);
     p.out_type = out_type;
     p.status = g.status_dev;
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g.device);
-    if (choose_mt(M, N, sms) == 2) {
-        dim3 grid((M + 255) / 256, N / 128);
-        q4k_linear_tc_kernel<2><<<grid, Layout<2>::kThreads, Layout<2>::kTotal, stream>>>(x_map, w_map, p);
-    } else {
-        dim3 grid((M + 127) / 128, N / 128);
-        q4k_linear_tc_kernel<1><<<grid, Layout<1>::kThreads, Layout<1>::kTotal, stream>>>(x_map, w_map, p);
-    }
+    CUtensorMap x_map, w_map;
+    if (!q3_encode_tmap_2d(&x_map, x_f16, K, M, 64, p.NT, error, error_len)) return false;
+    if (!q3_encode_tmap_bytes_2d(&w_map, weight, (uint64_t)(K / Q3_QUANT_QK_K) * kRawRowBytes,
+                                 N, kRawRowBytes, 128, error, error_len))
+        return false;
+    dim3 grid((M + p.NT - 1) / p.NT, N / 128);
+    q4k_linear_tc_kernel<<<grid, kThreads, kSmemTotal, stream>>>(x_map, w_map, p);
     Q3_LAUNCH_CHECK("q4k_linear_tc launch failed");
     return true;
 }
@@ -483,12 +449,8 @@ extern "C" bool q3_cuda_q4k_linear_init(int device, size_t max_tokens, int64_t m
         return q3_fail(error, error_len, "q3_q4_linear: no CUDA device");
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "q3_q4_linear: cudaSetDevice", e);
-    e = cudaFuncSetAttribute(q4k_linear_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)Layout<1>::kTotal);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(q4k_linear_tc_kernel<2>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)Layout<2>::kTotal);
+    e = cudaFuncSetAttribute(q4k_linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kSmemTotal);
     if (e == cudaSuccess) e = cudaGetSymbolAddress((void **)&g.status_dev, q3_linear_status_word);
     if (e == cudaSuccess) e = cudaMemset(g.status_dev, 0, sizeof(uint32_t));
     if (e == cudaSuccess && !g.ev_begin) {
