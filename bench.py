@@ -480,7 +480,8 @@ def random_q4k_weight(torch, n_features, k, device, seed=0):
     return w.view(n_features, -1)
 
 
-def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, reps=20):
+def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, reps=20,
+                    tiled=True):
     """Resident Q4_K projection next to the attention path (q/k/v projection of
     Qwen3-32B as one [10240, 5120] weight, or the output projection
     [5120, 8192]): f16 activations in, bf16 out, one kernel. Six weight copies
@@ -491,6 +492,9 @@ def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, rep
     geo = q4_linear.bind_geometry(K, N)
     copies = max(2, int(200e6 // geo.weight_bytes) + 1)
     ws = [random_q4k_weight(torch, N, K, device, seed=i) for i in range(copies)]
+    if tiled:   # one-time re-layout (q3_cuda_q4k_linear_pack), not timed
+        packed = [lin.pack(geo, w) for w in ws]
+        ws, geo = [t for t, _ in packed], packed[0][1]
     g = torch.Generator(device=device).manual_seed(1)
     x = torch.randn(M, K, generator=g, device=device).to(torch.float16)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=device)
@@ -509,6 +513,7 @@ def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, rep
     return {"ms": ms, "tflops": tf, "frac_of_burst_peak": tf / peaks["tflops_burst"],
             "tokens_per_s": M / (ms * 1e-3), "M": M, "N": N, "K": K,
             "weight_bytes": int(geo.weight_bytes), "status": lin.status(),
+            "weight_layout": "tiled (packed once)" if tiled else "GGUF row-major",
             "algorithmic_bytes": int(geo.weight_bytes + M * K * 2 + M * N * 2)}
 
 
@@ -517,6 +522,8 @@ CASES.update({
     "q4k_qkv_4096": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 4096, reps=reps),
     "q4k_oproj_2048": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 2048, 5120, 8192, reps),
     "q4k_qkv_16": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 16, reps=reps),
+    "q4k_qkv_4096_gguf_layout": lambda pkg, torch, dev, reps: case_q4k_linear(
+        pkg, torch, dev, 4096, reps=reps, tiled=False),
 })
 
 

@@ -8,8 +8,8 @@
  * Where the reference quantises the fp32 activations to Q8_1 and runs integer
  * MMQ/MMVQ kernels, this library converts them to f16 and runs one tensor-core
  * kernel (tcgen05, fp32 accumulation in tensor memory) that dequantises the
- * Q4_K blocks into f16 operands in shared memory; the result is closer to the
- * exact fp32 product than the reference's (no activation quantisation).
+ * Q4_K blocks into f16 operands held in tensor memory; the result is closer to
+ * the exact fp32 product than the reference's (no activation quantisation).
  *
  * Part 2 is native: f16 activations in, bf16/f16/fp32 out, no conversion pass.
  *
@@ -89,6 +89,18 @@ void q3_cuda_q4k_linear_read_stats(q3_q4_linear_stats *stats, void *stream);
 /* ---- part 2: native entry (no counterpart in the reference) -------------- */
 
 enum { Q3_OUT_F32 = 0, Q3_OUT_BF16 = 1, Q3_OUT_F16 = 2 };
+
+/* One-time re-layout of a resident Q4_K weight (same bytes, same size): the
+ * 128 blocks that one 128-feature tile needs for one 256-wide k range are
+ * stored back to back (18432 contiguous bytes), tile by tile, so that the
+ * kernel fetches them with one dense TMA box instead of 128 strided 144-byte
+ * rows. `tiled_geometry` receives the geometry to pass with the tiled copy
+ * (qtype Q3_QUANT_Q4_K_TILED); both linear entry points accept either layout.
+ * The source may be freed afterwards. */
+#define Q3_QUANT_Q4_K_TILED (12u | (1u << 16))
+bool q3_cuda_q4k_linear_pack(const q3_q4_linear_geometry *geometry, const void *weight,
+                             void *tiled, q3_q4_linear_geometry *tiled_geometry,
+                             void *stream, char *error, size_t error_len);
 
 /* x: f16 [tokens][K] row-major (16-byte aligned); out: [tokens][N] of out_type.
  * One kernel launch, no workspace. q3_cuda_q4k_linear_init must have run on

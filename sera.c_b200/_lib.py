@@ -51,6 +51,7 @@ def bind_linear(L):
     sig("q3_cuda_q4k_linear", b, [gp, vp, vp, sz, vp, vp, sp] + err)
     sig("q3_cuda_q4k_linear_read_stats", None, [sp, vp])
     sig("q3_cuda_q4k_linear_f16", b, [gp, vp, vp, sz, vp, u32, vp] + err)
+    sig("q3_cuda_q4k_linear_pack", b, [gp, vp, vp, gp, vp] + err)
     sig("q3_cuda_q4k_linear_status", b, [vp, ctypes.POINTER(u32)] + err)
     return L
 

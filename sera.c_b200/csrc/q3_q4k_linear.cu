@@ -49,6 +49,7 @@ using namespace q3ptx;
 constexpr uint32_t kRawRowBytes = Q3_QUANT_Q4_K_BLOCK_BYTES;
 constexpr uint32_t kRawBytes = 128 * kRawRowBytes; /* 128 feature rows, one block each */
 constexpr uint32_t kRawStages = 2;
+constexpr uint32_t kTiledRows = kRawBytes / 256;   /* tiled layout: a chunk = 72 rows of 256 B */
 constexpr uint32_t kMaxTokens = 256;               /* token tile = MMA N */
 constexpr uint32_t kXStageBytes = kMaxTokens * 128; /* [256 tokens][64 k] f16 */
 constexpr uint32_t kXStages = 5;
@@ -69,7 +70,7 @@ struct Misc {
     uint64_t raw_full[kRawStages], raw_empty[kRawStages];
     uint64_t x_full[kXStages], x_empty[kXStages];
     uint64_t a_full[kAStages], a_empty[kAStages];
-    uint64_t acc_full;
+    uint64_t acc_full, d_free;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -79,6 +80,7 @@ struct LinearParams {
     void *out;
     uint32_t M, N, K;
     uint32_t NT;          /* tokens per CTA: multiple of 16, <= 256 */
+    uint32_t w_tiled;     /* weight in the tiled layout of q3_cuda_q4k_linear_pack */
     uint32_t out_type;
     uint32_t *status;
 };
@@ -111,6 +113,34 @@ __device__ __forceinline__ uint32_t dequant_hi(uint32_t pair, __half2 scale,
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+/* One output row segment: 32 token columns of one feature (lane) - the 32 lanes
+ * of a warp store 32 consecutive features of one token per instruction. */
+__device__ __forceinline__ void store_chunk(const LinearParams &p, const uint32_t *v,
+                                            uint32_t m0, uint32_t t0, uint32_t feature) {
+#pragma unroll
+    for (uint32_t i = 0; i < 32; i++) {
+        const uint32_t t = t0 + i;
+        const uint32_t token = m0 + t;
+        if (t < p.NT && token < p.M) {
+            const size_t off = (size_t)token * p.N + feature;
+            const float f = __uint_as_float(v[i]);
+            if (p.out_type == Q3_OUT_F32)
+                static_cast<float *>(p.out)[off] = f;
+            else if (p.out_type == Q3_OUT_BF16)
+                static_cast<__nv_bfloat16 *>(p.out)[off] = __float2bfloat16_rn(f);
+            else
+                static_cast<__half *>(p.out)[off] = __float2half_rn(f);
+        }
+    }
+}
+
+/* Persistent: CTA b computes output tiles b, b + gridDim.x, ... (tile = token
+ * tile fastest, then feature tile). All rings run on counters that continue
+ * across tiles, so the producers and the dequantising groups flow from one
+ * tile into the next; only the accumulator D is single: a tile's first MMA
+ * waits until every thread has read the previous tile's D out of tensor
+ * memory (d_free). A group reads D after it has already converted its next two
+ * k-steps, so the MMA has operands to go on with while the rows are stored. */
 __global__ void __launch_bounds__(kThreads, 1)
 q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                      const __grid_constant__ CUtensorMap w_map, const LinearParams p) {
@@ -119,10 +149,12 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
     Misc *misc = reinterpret_cast<Misc *>(smem + kSmemMisc);
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t m0 = blockIdx.x * p.NT;
-    const uint32_t n0 = blockIdx.y * 128u;
     const uint32_t n_super = p.K / Q3_QUANT_QK_K;   /* Q4_K blocks per feature row */
-    const uint32_t n_kt = n_super * 4u;             /* k-steps of 64 */
+    const uint32_t n_kt = n_super * 4u;             /* k-steps of 64 per tile */
+    const uint32_t n_tok_tiles = (p.M + p.NT - 1u) / p.NT;
+    const uint32_t n_tiles = n_tok_tiles * (p.N / 128u);
+    const uint32_t n_my = blockIdx.x < n_tiles
+                              ? (n_tiles - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kRawStages; s++) {
@@ -138,6 +170,7 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             mbar_init(&misc->a_empty[s], 1);
         }
         mbar_init(&misc->acc_full, 1);
+        mbar_init(&misc->d_free, 128 * kGroups);
         misc->abort_flag = 0;
         fence_mbar_init();
     }
@@ -155,13 +188,18 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
         if (lane == 0) {
             prefetch_tmap(&x_map);
             bool alive = true;
-            for (uint32_t kt = 0; kt < n_kt && alive; kt++) {
-                const uint32_t s = kt % kXStages, use = kt / kXStages;
-                if (use > 0) alive = wait_or_abort(&misc->x_empty[s], (use - 1) & 1u, misc);
-                if (!alive) break;
-                mbar_arrive_expect_tx(&misc->x_full[s], p.NT * 128u);
-                tma_load_2d(smem + kSmemX + s * kXStageBytes, &x_map, (int32_t)(kt * 64u),
-                            (int32_t)m0, &misc->x_full[s]);
+            uint32_t g = 0;   /* k-steps issued by this CTA so far */
+            for (uint32_t ti = 0; ti < n_my && alive; ti++) {
+                const uint32_t tile = blockIdx.x + ti * gridDim.x;
+                const uint32_t m0 = (tile % n_tok_tiles) * p.NT;
+                for (uint32_t kt = 0; kt < n_kt; kt++, g++) {
+                    const uint32_t s = g % kXStages, use = g / kXStages;
+                    if (use > 0) alive = wait_or_abort(&misc->x_empty[s], (use - 1) & 1u, misc);
+                    if (!alive) break;
+                    mbar_arrive_expect_tx(&misc->x_full[s], p.NT * 128u);
+                    tma_load_2d(smem + kSmemX + s * kXStageBytes, &x_map, (int32_t)(kt * 64u),
+                                (int32_t)m0, &misc->x_full[s]);
+                }
             }
         }
         __syncwarp();
@@ -170,13 +208,25 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
         if (lane == 0) {
             prefetch_tmap(&w_map);
             bool alive = true;
-            for (uint32_t sb = 0; sb < n_super && alive; sb++) {
-                const uint32_t rs = sb % kRawStages, use = sb / kRawStages;
-                if (use > 0) alive = wait_or_abort(&misc->raw_empty[rs], (use - 1) & 1u, misc);
-                if (!alive) break;
-                mbar_arrive_expect_tx(&misc->raw_full[rs], kRawBytes);
-                tma_load_2d(smem + kSmemRaw + rs * kRawBytes, &w_map,
-                            (int32_t)(sb * kRawRowBytes), (int32_t)n0, &misc->raw_full[rs]);
+            uint32_t g = 0;   /* super-blocks issued so far */
+            for (uint32_t ti = 0; ti < n_my && alive; ti++) {
+                const uint32_t tile = blockIdx.x + ti * gridDim.x;
+                const uint32_t n0 = (tile / n_tok_tiles) * 128u;
+                for (uint32_t sb = 0; sb < n_super; sb++, g++) {
+                    const uint32_t rs = g % kRawStages, use = g / kRawStages;
+                    if (use > 0)
+                        alive = wait_or_abort(&misc->raw_empty[rs], (use - 1) & 1u, misc);
+                    if (!alive) break;
+                    mbar_arrive_expect_tx(&misc->raw_full[rs], kRawBytes);
+                    if (p.w_tiled)   /* 18432 contiguous bytes = 72 rows of 256 */
+                        tma_load_2d(smem + kSmemRaw + rs * kRawBytes, &w_map, 0,
+                                    (int32_t)(((n0 / 128u) * n_super + sb) * kTiledRows),
+                                    &misc->raw_full[rs]);
+                    else
+                        tma_load_2d(smem + kSmemRaw + rs * kRawBytes, &w_map,
+                                    (int32_t)(sb * kRawRowBytes), (int32_t)n0,
+                                    &misc->raw_full[rs]);
+                }
             }
         }
         __syncwarp();
@@ -186,39 +236,88 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             const uint32_t idesc = umma_idesc_f16(128, p.NT, false);
             const uint32_t x_addr = smem_u32(smem + kSmemX);
             bool alive = true;
-            for (uint32_t kt = 0; kt < n_kt; kt++) {
-                const uint32_t sx = kt % kXStages, sa = kt % kAStages;
-                alive = wait_or_abort(&misc->x_full[sx], (kt / kXStages) & 1u, misc) &&
-                        wait_or_abort(&misc->a_full[sa], (kt / kAStages) & 1u, misc);
-                if (!alive) break;
-                tc_fence_after();
+            uint32_t g = 0;
+            for (uint32_t ti = 0; ti < n_my && alive; ti++) {
+                if (ti > 0) {
+                    alive = wait_or_abort(&misc->d_free, (ti - 1) & 1u, misc);
+                    if (!alive) break;
+                    tc_fence_after();
+                }
+                for (uint32_t kt = 0; kt < n_kt; kt++, g++) {
+                    const uint32_t sx = g % kXStages, sa = g % kAStages;
+                    alive = wait_or_abort(&misc->x_full[sx], (g / kXStages) & 1u, misc) &&
+                            wait_or_abort(&misc->a_full[sa], (g / kAStages) & 1u, misc);
+                    if (!alive) break;
+                    tc_fence_after();
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; kk++)
-                    umma_ts(tmem + kColD, tmem + kColA + sa * 32u + kk * 8u,
-                            umma_desc(x_addr + sx * kXStageBytes + kk * 32u, 16, 1024), idesc,
-                            (kt | kk) != 0u);
-                umma_commit(&misc->x_empty[sx]);
-                umma_commit(&misc->a_empty[sa]);
+                    for (uint32_t kk = 0; kk < 4; kk++)
+                        umma_ts(tmem + kColD, tmem + kColA + sa * 32u + kk * 8u,
+                                umma_desc(x_addr + sx * kXStageBytes + kk * 32u, 16, 1024),
+                                idesc, (kt | kk) != 0u);
+                    umma_commit(&misc->x_empty[sx]);
+                    umma_commit(&misc->a_empty[sa]);
+                }
+                if (alive) umma_commit(&misc->acc_full);
             }
-            if (alive) umma_commit(&misc->acc_full);
         }
         __syncwarp();
     } else if (warp >= 4) {
-        /* ============ dequantise into tensor memory, then drain D ============
-         * Group g (128 threads, one per feature row) converts k-steps g, g+3,
-         * ...: the groups work on different k-steps at the same time, which
-         * hides the latency of one step's wait -> load -> convert -> store. */
+        /* ============ dequantise into tensor memory; drain D ============
+         * Group g (128 threads, one per feature row) converts this CTA's
+         * k-steps g, g+3, ... (counted across tiles): the groups work on
+         * different k-steps at the same time, which hides the latency of one
+         * step's wait -> load -> convert -> store chain. */
         const uint32_t dq = threadIdx.x - 128u;
         const uint32_t row = dq & 127u;              /* feature row = tensor-memory lane */
         const uint32_t group = dq >> 7;
         const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
+        const uint32_t n_chunks = (p.NT + 31u) / 32u;
         const uint8_t *blk = nullptr;
         uint4 hdr = make_uint4(0, 0, 0, 0);
         float dd = 0.f, dm = 0.f;
         uint32_t cur_sb = 0xffffffffu;
         bool alive = true;
-        for (uint32_t kt = group; kt < n_kt; kt += kGroups) {
-            const uint32_t sb = kt >> 2, j = kt & 3u;
+
+        /* Read this thread's share of tile ti's D, release D, store the rows. */
+        auto drain = [&](uint32_t ti) {
+            if (alive) alive = wait_or_abort(&misc->acc_full, ti & 1u, misc);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) return;
+            tc_fence_after();
+            const uint32_t tile = blockIdx.x + ti * gridDim.x;
+            const uint32_t m0 = (tile % n_tok_tiles) * p.NT;
+            const uint32_t feature = (tile / n_tok_tiles) * 128u + row;
+            uint32_t ch = group;
+            for (; ch + kGroups < n_chunks; ch += kGroups) {
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + kColD + ch * 32u, v);
+                tmem_wait_ld();
+                store_chunk(p, v, m0, ch * 32u, feature);
+            }
+            /* last chunk of this thread: release D before storing */
+            uint32_t v[32];
+            const bool mine = ch < n_chunks;
+            if (mine) {
+                tmem_ld32(tmem + lane_base + kColD + ch * 32u, v);
+                tmem_wait_ld();
+            }
+            tc_fence_before();
+            mbar_arrive(&misc->d_free);
+            if (mine) store_chunk(p, v, m0, ch * 32u, feature);
+        };
+
+        const uint32_t total = n_my * n_kt;
+        uint32_t cur_ti = 0, pending = 0xffffffffu, ahead = 0;
+        for (uint32_t g = group; g < total && alive; g += kGroups) {
+            const uint32_t ti = g / n_kt;
+            if (ti != cur_ti) {
+                if (pending != 0xffffffffu) drain(pending);   /* (only for very short K) */
+                pending = cur_ti;
+                ahead = 0;
+                cur_ti = ti;
+                if (!alive) break;
+            }
+            const uint32_t sb = g >> 2, j = g & 3u;   /* n_kt is a multiple of 4 */
             if (sb != cur_sb) {
                 if (cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
                 const uint32_t rs = sb % kRawStages;
@@ -268,7 +367,7 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                 v[16 + 2 * u] = dequant_hi(p01, scale_hi, noff_hi);
                 v[16 + 2 * u + 1] = dequant_hi(p23, scale_hi, noff_hi);
             }
-            const uint32_t sa = kt % kAStages, use = kt / kAStages;
+            const uint32_t sa = g % kAStages, use = g / kAStages;
             if (use > 0) alive = wait_or_abort(&misc->a_empty[sa], (use - 1) & 1u, misc);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
@@ -277,44 +376,35 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&misc->a_full[sa]);
-        }
-        if (alive && cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
-
-        if (alive) alive = wait_or_abort(&misc->acc_full, 0u, misc);
-        alive = __all_sync(0xffffffffu, alive);
-        if (alive) {
-            tc_fence_after();
-            /* lane = feature, column = token: the 32 lanes of a warp store 32
-             * consecutive features of one token per instruction */
-            const uint32_t feature = n0 + row;
-            const uint32_t n_chunks = (p.NT + 31u) / 32u;
-            for (uint32_t ch = group; ch < n_chunks; ch += kGroups) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + kColD + ch * 32u, v);
-                tmem_wait_ld();
-#pragma unroll
-                for (uint32_t i = 0; i < 32; i++) {
-                    const uint32_t t = ch * 32u + i;
-                    const uint32_t token = m0 + t;
-                    if (t < p.NT && token < p.M) {
-                        const size_t off = (size_t)token * p.N + feature;
-                        const float f = __uint_as_float(v[i]);
-                        if (p.out_type == Q3_OUT_F32)
-                            static_cast<float *>(p.out)[off] = f;
-                        else if (p.out_type == Q3_OUT_BF16)
-                            static_cast<__nv_bfloat16 *>(p.out)[off] = __float2bfloat16_rn(f);
-                        else
-                            static_cast<__half *>(p.out)[off] = __float2half_rn(f);
-                    }
-                }
+            if (pending != 0xffffffffu && ++ahead == 2) {
+                drain(pending);
+                pending = 0xffffffffu;
             }
         }
+        if (alive && cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
+        if (pending != 0xffffffffu) drain(pending);
+        if (n_my > 0) drain(n_my - 1);
     }
 
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && misc->abort_flag) atomicOr(p.status, 1u);
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+/* GGUF row-major blocks -> tiled: chunk (feature tile, super-block) holds the 128
+ * blocks of its rows back to back. One thread per 16 bytes. */
+__global__ void q4k_pack_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst,
+                                uint32_t n_rows, uint32_t n_super) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)n_rows * n_super * 9u;
+    if (i >= total) return;
+    const uint32_t part = (uint32_t)(i % 9u);
+    const size_t blk = i / 9u;
+    const uint32_t sb = (uint32_t)(blk % n_super);
+    const uint32_t row = (uint32_t)(blk / n_super);
+    const size_t chunk = (size_t)(row / 128u) * n_super + sb;
+    dst[(chunk * 128u + (row % 128u)) * 9u + part] = src[i];
 }
 
 /* fp32 -> f16, 8 elements per thread (n is a multiple of 256: K is). */
@@ -375,7 +465,7 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
                    size_t tokens, void *out, uint32_t out_type, cudaStream_t stream,
                    char *error, size_t error_len) {
     const uint32_t M = (uint32_t)tokens, N = (uint32_t)geo->N, K = (uint32_t)geo->K;
-    if (geo->qtype != Q3_QUANT_Q4_K)
+    if (geo->qtype != Q3_QUANT_Q4_K && geo->qtype != Q3_QUANT_Q4_K_TILED)
         return q3_fail(error, error_len,
                        "q3_q4_linear: only Q4_K weights are implemented (Q6_K is not)");
     if (K % Q3_QUANT_QK_K || N % 128u)
@@ -393,12 +483,20 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
     p.NT = choose_token_tile(M, N, sms);
     p.out_type = out_type;
     p.status = g.status_dev;
+    p.w_tiled = geo->qtype == Q3_QUANT_Q4_K_TILED ? 1u : 0u;
     CUtensorMap x_map, w_map;
     if (!q3_encode_tmap_2d(&x_map, x_f16, K, M, 64, p.NT, error, error_len)) return false;
-    if (!q3_encode_tmap_bytes_2d(&w_map, weight, (uint64_t)(K / Q3_QUANT_QK_K) * kRawRowBytes,
-                                 N, kRawRowBytes, 128, error, error_len))
+    const uint64_t row_bytes = (uint64_t)(K / Q3_QUANT_QK_K) * kRawRowBytes;
+    if (p.w_tiled) {
+        if (!q3_encode_tmap_bytes_2d(&w_map, weight, 256, row_bytes * N / 256, 256, kTiledRows,
+                                     error, error_len))
+            return false;
+    } else if (!q3_encode_tmap_bytes_2d(&w_map, weight, row_bytes, N, kRawRowBytes, 128, error,
+                                        error_len)) {
         return false;
-    dim3 grid((M + p.NT - 1) / p.NT, N / 128);
+    }
+    const uint32_t n_tiles = ((M + p.NT - 1) / p.NT) * (N / 128);
+    const uint32_t grid = n_tiles < (uint32_t)sms ? n_tiles : (uint32_t)sms;
     q4k_linear_tc_kernel<<<grid, kThreads, kSmemTotal, stream>>>(x_map, w_map, p);
     Q3_LAUNCH_CHECK("q4k_linear_tc launch failed");
     return true;
@@ -551,6 +649,31 @@ extern "C" bool q3_cuda_q4k_linear_f16(const q3_q4_linear_geometry *geometry,
     if (out_type > Q3_OUT_F16) return q3_fail(error, error_len, "q3_q4_linear: bad output type");
     return launch_linear(geometry, weight, x_f16, token_count, out, out_type,
                          (cudaStream_t)stream, error, error_len);
+}
+
+extern "C" bool q3_cuda_q4k_linear_pack(const q3_q4_linear_geometry *geometry,
+                                        const void *weight, void *tiled,
+                                        q3_q4_linear_geometry *tiled_geometry, void *stream,
+                                        char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!geometry || !weight || !tiled || !tiled_geometry)
+        return q3_fail(error, error_len, "q3_q4_linear: null argument");
+    if (geometry->qtype != Q3_QUANT_Q4_K)
+        return q3_fail(error, error_len, "q3_q4_linear: pack takes a Q4_K weight in GGUF order");
+    if (geometry->N <= 0 || geometry->K <= 0 || geometry->N % 128 || geometry->K % Q3_QUANT_QK_K)
+        return q3_fail(error, error_len,
+                       "q3_q4_linear: K must be a multiple of 256 and N of 128");
+    if (((uintptr_t)weight | (uintptr_t)tiled) & 15u)
+        return q3_fail(error, error_len, "q3_q4_linear: pointers must be 16-byte aligned");
+    const uint32_t n_super = (uint32_t)geometry->K / Q3_QUANT_QK_K;
+    const size_t total = (size_t)geometry->N * n_super * 9u;
+    q4k_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        static_cast<const uint4 *>(weight), static_cast<uint4 *>(tiled), (uint32_t)geometry->N,
+        n_super);
+    Q3_LAUNCH_CHECK("q3_q4_linear: pack launch failed");
+    *tiled_geometry = *geometry;
+    tiled_geometry->qtype = Q3_QUANT_Q4_K_TILED;
+    return true;
 }
 
 extern "C" bool q3_cuda_q4k_linear_status(void *stream, uint32_t *status, char *error,

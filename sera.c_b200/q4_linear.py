@@ -69,6 +69,14 @@ class Q4Linear:
               tokens, out.data_ptr(), code, stream)
         return out
 
+    def pack(self, geo, weight, stream=None):
+        """q3_cuda_q4k_linear_pack: returns (tiled weight, tiled geometry)."""
+        tiled = self.torch.empty_like(weight)
+        tg = LinearGeometry()
+        _call(_L().q3_cuda_q4k_linear_pack, ctypes.byref(geo), weight.data_ptr(),
+              tiled.data_ptr(), ctypes.byref(tg), stream)
+        return tiled, tg
+
     def status(self, stream=None):
         s = ctypes.c_uint32(0)
         _call(_L().q3_cuda_q4k_linear_status, stream, ctypes.byref(s))

@@ -58,6 +58,28 @@ def test_f16_entry_matches_oracle(lin, M, N, K):
             assert exact["rel_l2"] < 1e-3 and exact["cos"] > 0.99999, exact
 
 
+@pytest.mark.parametrize("M,N,K", [(5, 128, 256), (200, 384, 1024), (700, 1024, 2560)])
+def test_tiled_weight_layout_is_bit_identical(lin, M, N, K):
+    """q3_cuda_q4k_linear_pack: same bytes regrouped per (feature tile, 256-wide
+    k range); the linear gives bit-identical output from either layout, and the
+    tiled buffer is a permutation of the 144-byte blocks."""
+    q4, L = lin
+    w, x = _case(3 * M + N, M, N, K)
+    geo = q4.bind_geometry(K, N)
+    wd = torch.from_numpy(w).cuda()
+    xd = torch.from_numpy(x).cuda().half()
+    tiled, tgeo = L.pack(geo, wd)
+    assert tgeo.qtype == (12 | (1 << 16)) and tgeo.N == N and tgeo.K == K
+    a = L.linear_f16(geo, wd, xd, out_dtype=torch.float32)
+    b = L.linear_f16(tgeo, tiled, xd, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    nsb = K // 256
+    want = w.reshape(N // 128, 128, nsb, 144).transpose(0, 2, 1, 3).reshape(-1)
+    assert np.array_equal(tiled.cpu().numpy().reshape(-1), want)
+    assert L.status() == 0
+
+
 def test_rows_beyond_the_batch_are_untouched(lin):
     q4, L = lin
     w, x = _case(9, 70, 256, 512)
