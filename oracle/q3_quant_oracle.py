@@ -117,6 +117,76 @@ def q4k_linear(weight_bytes, x, operands="fp32"):
     return xx @ w.T
 
 
+# --------------------------------------------------------------------------
+# Q6_K (the output.weight of a Q4_K_M file) and the selected-row LM head
+# --------------------------------------------------------------------------
+Q6_K_BLOCK_BYTES = 210
+
+
+def q6k_dequantize(blocks):
+    """fp32 values of Q6_K blocks as the reference's scalar loop produces them
+    (src/q3_quant.c:78-103): per block ql[128] low nibbles, qh[64] high 2 bits,
+    scales[16] int8, d (f16); per half of 128 elements and l in 0..31
+        q1 = (ql[l]    & 15 | (qh[l]      & 3) << 4) - 32 -> element l
+        q2 = (ql[l+32] & 15 | (qh[l] >> 2 & 3) << 4) - 32 -> element l + 32
+        q3 = (ql[l]   >> 4  | (qh[l] >> 4 & 3) << 4) - 32 -> element l + 64
+        q4 = (ql[l+32] >> 4 | (qh[l] >> 6 & 3) << 4) - 32 -> element l + 96
+    value = d * scale[is + 0/2/4/6] * q with is = l / 16; the products are
+    formed left to right in fp32."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    if b.size % Q6_K_BLOCK_BYTES:
+        raise ValueError("Q6_K data must be a whole number of 210-byte blocks")
+    b = b.reshape(-1, Q6_K_BLOCK_BYTES)
+    n = b.shape[0]
+    ql = b[:, 0:128].reshape(n, 2, 64).astype(np.int32)
+    qh = b[:, 128:192].reshape(n, 2, 32).astype(np.int32)
+    sc = b[:, 192:208].copy().view(np.int8).reshape(n, 2, 8).astype(np.float32)
+    d = b[:, 208:210].copy().view(np.float16).astype(np.float32)[:, 0]
+    out = np.empty((n, 2, 128), np.float32)
+    l = np.arange(32)
+    is_ = l // 16
+    for q, (lo, shift_q, nib_hi, sc_off) in enumerate(
+            [(0, 0, False, 0), (32, 2, False, 2), (0, 4, True, 4), (32, 6, True, 6)]):
+        low = ql[:, :, lo:lo + 32]
+        low = (low >> 4) if nib_hi else (low & 0xF)
+        val = (low | (((qh >> shift_q) & 3) << 4)) - 32
+        scale = sc[:, :, is_ + sc_off]
+        t = (d[:, None, None] * scale).astype(np.float32)
+        out[:, :, 32 * q:32 * q + 32] = (t * val.astype(np.float32)).astype(np.float32)
+    return out.reshape(-1)
+
+
+def q6k_random_blocks(rng, n_blocks, d_max=0.002):
+    b = rng.integers(0, 256, (n_blocks, Q6_K_BLOCK_BYTES), dtype=np.uint8)
+    d = (rng.random(n_blocks) * d_max + d_max * 0.1).astype(np.float16)
+    b[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
+    return b
+
+
+def dequantize_rows(weight_bytes, qtype):
+    """[rows, row_bytes] quantised rows -> [rows, K] fp32."""
+    rows = weight_bytes.shape[0]
+    f = q4k_dequantize if qtype == Q4_K_TYPE else q6k_dequantize
+    return f(weight_bytes).reshape(rows, -1)
+
+
+def gather_last_rows(src, branch_offsets):
+    """out[b] = src[branch_offsets[b+1] - 1]  (src/q3_forward.cu:553-564)."""
+    idx = np.asarray(branch_offsets[1:], np.int64) - 1
+    return np.asarray(src)[idx]
+
+
+def candidate_logits_batched(hidden_per_branch, weight_bytes, qtype, candidate_ids,
+                             candidate_count):
+    """logits[b*K + c] = dot(row(candidate_ids[b*K + c]), hidden_per_branch[b]) in
+    double (the reference sums fp32 products in a tree: src/q3_forward.cu:566-607)."""
+    ids = np.asarray(candidate_ids, np.int64)
+    w = dequantize_rows(weight_bytes[ids], qtype).astype(np.float64)
+    h = np.asarray(hidden_per_branch, np.float32).astype(np.float64)
+    b = np.arange(ids.size) // candidate_count
+    return np.einsum("ik,ik->i", w, h[b])
+
+
 def linear_error_metrics(got, ref):
     """The figures the reference's test prints and checks."""
     got = np.asarray(got, np.float64).reshape(-1)

@@ -53,6 +53,12 @@ def bind_linear(L):
     sig("q3_cuda_q4k_linear_f16", b, [gp, vp, vp, sz, vp, u32, vp] + err)
     sig("q3_cuda_q4k_linear_pack", b, [gp, vp, vp, gp, vp] + err)
     sig("q3_cuda_q4k_linear_status", b, [vp, ctypes.POINTER(u32)] + err)
+    # include/q3_lmhead.h
+    sig("q3_cuda_gather_last_rows", b, [vp, vp, u32, u32, vp, vp] + err)
+    sig("q3_cuda_candidate_logits_batched", b,
+        [vp, vp, u32, u32, u32, vp, u32, u32, vp, vp] + err)
+    sig("q3_cuda_candidate_head", b,
+        [vp, vp, vp, u32, u32, u32, vp, u32, u32, vp, vp, vp] + err)
     return L
 
 

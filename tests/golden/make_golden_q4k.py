@@ -46,6 +46,20 @@ def main():
     np.savez(path, blocks=blocks, values=out)
     print(path, os.path.getsize(path), "bytes")
 
+    # Q6_K (210-byte blocks; ref: src/q3_quant.c:78-103): 5 random + all-zero + all-ones
+    b6 = rng.integers(0, 256, (7, 210), dtype=np.uint8)
+    for i in range(5):
+        b6[i, 208:210] = np.asarray([rng.random() * 0.01 + 1e-4], np.float16).view(np.uint8)
+    b6[5] = 0
+    b6[6] = 255
+    b6[6, 208:210] = np.asarray([0.25], np.float16).view(np.uint8)
+    out6 = np.zeros(7 * 256, np.float32)
+    ok = lib.q3_quant_dequantize_row(14, b6.ctypes.data, 7, out6.ctypes.data, out6.size, err, 256)
+    assert ok, err.value
+    path = os.path.join(HERE, "q6k_dequant_ref.npz")
+    np.savez(path, blocks=b6, values=out6)
+    print(path, os.path.getsize(path), "bytes")
+
 
 if __name__ == "__main__":
     main()

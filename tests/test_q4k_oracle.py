@@ -93,3 +93,23 @@ def test_linear_oracle_small():
             assert abs(out[t, n] - float(np.dot(deq[n], x[t].astype(np.float64)))) < 1e-9
     m = qo.linear_error_metrics(qo.q4k_linear(w, x, operands="f16"), out)
     assert m["rel_l2"] < 2e-3 and m["cos"] > 0.99999
+
+
+def test_q6k_dequant_matches_reference_fixture_bit_exactly():
+    g = np.load(os.path.join(ROOT, "tests", "golden", "q6k_dequant_ref.npz"))
+    got = qo.q6k_dequantize(g["blocks"])
+    assert np.array_equal(got.view(np.uint32), g["values"].view(np.uint32))
+
+
+def test_candidate_head_oracle_small():
+    rng = np.random.default_rng(1)
+    w = qo.q6k_random_blocks(rng, 6 * 2).reshape(6, -1)
+    rows = rng.standard_normal((5, 512)).astype(np.float32)
+    offs = np.asarray([0, 2, 5], np.int32)
+    last = qo.gather_last_rows(rows, offs)
+    assert np.array_equal(last, rows[[1, 4]])
+    ids = np.asarray([0, 5, 3, 3], np.int32)
+    out = qo.candidate_logits_batched(last, w, 14, ids, 2)
+    deq = qo.q6k_dequantize(w).reshape(6, 512).astype(np.float64)
+    assert abs(out[1] - float(deq[5] @ rows[1].astype(np.float64))) < 1e-9
+    assert abs(out[2] - float(deq[3] @ rows[4].astype(np.float64))) < 1e-9
