@@ -278,8 +278,19 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
         uint32_t cur_sb = 0xffffffffu;
         bool alive = true;
 
+        uint32_t stored = 0xffffffffu;   /* A stage whose store is issued but not yet published */
+        auto publish = [&]() {
+            if (stored != 0xffffffffu) {
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&misc->a_full[stored]);
+                stored = 0xffffffffu;
+            }
+        };
+
         /* Read this thread's share of tile ti's D, release D, store the rows. */
         auto drain = [&](uint32_t ti) {
+            publish();
             if (alive) alive = wait_or_abort(&misc->acc_full, ti & 1u, misc);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) return;
@@ -367,20 +378,23 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                 v[16 + 2 * u] = dequant_hi(p01, scale_hi, noff_hi);
                 v[16 + 2 * u + 1] = dequant_hi(p23, scale_hi, noff_hi);
             }
+            /* The store of the previous step has had this step's conversion
+             * time to retire: publish it now, then issue this step's store and
+             * go on without waiting for it. */
+            publish();
             const uint32_t sa = g % kAStages, use = g / kAStages;
             if (use > 0) alive = wait_or_abort(&misc->a_empty[sa], (use - 1) & 1u, misc);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
             tmem_st32(tmem + lane_base + kColA + sa * 32u, v);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&misc->a_full[sa]);
+            stored = sa;
             if (pending != 0xffffffffu && ++ahead == 2) {
                 drain(pending);
                 pending = 0xffffffffu;
             }
         }
+        if (alive) publish();
         if (alive && cur_sb != 0xffffffffu) mbar_arrive(&misc->raw_empty[cur_sb % kRawStages]);
         if (pending != 0xffffffffu) drain(pending);
         if (n_my > 0) drain(n_my - 1);
