@@ -787,6 +787,11 @@ def run_reference(args):
     t = float(np.mean(times))
     tokens = nb * SUFFIX
     value = tokens / (t * L)
+    # the same port on one thread (one branch of one layer), for the scalar figure
+    t_single, _ = cpu_sample(1, threads=1)
+    single = {"value": SUFFIX / (t_single * L), "unit": UNIT, "cores": 1, "kind": "port",
+              "sample": "1 of %d layers, 1 of %d branches x %d tokens, %.1f s"
+                        % (L, BRANCHES, SUFFIX, t_single)}
     sample = ("1 of %d layers, %d of %d branches x %d tokens over the full %d-token prefix "
               "per step; scaled by the layer count" % (L, nb, BRANCHES, SUFFIX, PREFIX))
     print(json.dumps({
@@ -800,7 +805,7 @@ def run_reference(args):
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "cpu_baseline_single_thread": single,
         **({} if args.no_ref_gpu else {"reference_gpu_kernels": reference_gpu_kernels(),
                                        "python_path_cpu": python_path_baseline()})}))
 

@@ -110,6 +110,18 @@ bool q3_cuda_q4k_linear_f16(const q3_q4_linear_geometry *geometry, const void *w
                             uint32_t out_type, void *stream, char *error,
                             size_t error_len);
 
+/* Host-only: the launch shape the linear picks for a batch (tokens per CTA =
+ * the MMA N dimension, a multiple of 16 up to 256; 128 features per tile;
+ * persistent CTAs, tile t -> CTA t % ctas). Pure arithmetic, no CUDA call. */
+typedef struct {
+    uint32_t token_tile;
+    uint32_t tiles;
+    uint32_t ctas;
+    uint32_t tiles_per_cta_max;
+} q3_q4_linear_plan_info;
+bool q3_q4_linear_plan(uint32_t tokens, uint32_t n_features, uint32_t sm_count,
+                       q3_q4_linear_plan_info *out, char *error, size_t error_len);
+
 /* Device status word of the linear kernels (bit 0: a bounded wait inside a
  * kernel gave up). Synchronises `stream`. */
 bool q3_cuda_q4k_linear_status(void *stream, uint32_t *status, char *error,

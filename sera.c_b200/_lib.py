@@ -30,6 +30,12 @@ class LinearStats(ctypes.Structure):
                 ("host_syncs", ctypes.c_uint64)]
 
 
+class LinearPlanInfo(ctypes.Structure):
+    """q3_q4_linear_plan_info"""
+    _fields_ = [("token_tile", ctypes.c_uint32), ("tiles", ctypes.c_uint32),
+                ("ctas", ctypes.c_uint32), ("tiles_per_cta_max", ctypes.c_uint32)]
+
+
 def bind_linear(L):
     """Signatures of include/q3_q4_linear.h (also valid for a build of the
     reference's own q3_q4_linear, which exports part 1 under the same names)."""
@@ -51,6 +57,7 @@ def bind_linear(L):
     sig("q3_cuda_q4k_linear", b, [gp, vp, vp, sz, vp, vp, sp] + err)
     sig("q3_cuda_q4k_linear_read_stats", None, [sp, vp])
     sig("q3_cuda_q4k_linear_f16", b, [gp, vp, vp, sz, vp, u32, vp] + err)
+    sig("q3_q4_linear_plan", b, [u32, u32, u32, ctypes.POINTER(LinearPlanInfo)] + err)
     sig("q3_cuda_q4k_linear_pack", b, [gp, vp, vp, gp, vp] + err)
     sig("q3_cuda_q4k_linear_status", b, [vp, ctypes.POINTER(u32)] + err)
     # include/q3_lmhead.h

@@ -690,6 +690,19 @@ extern "C" bool q3_cuda_q4k_linear_pack(const q3_q4_linear_geometry *geometry,
     return true;
 }
 
+extern "C" bool q3_q4_linear_plan(uint32_t tokens, uint32_t n_features, uint32_t sm_count,
+                                  q3_q4_linear_plan_info *out, char *error,
+                                  size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!out || tokens == 0 || n_features == 0 || n_features % 128u || sm_count == 0)
+        return q3_fail(error, error_len, "q3_q4_linear_plan: invalid argument");
+    out->token_tile = choose_token_tile(tokens, n_features, (int)sm_count);
+    out->tiles = ((tokens + out->token_tile - 1) / out->token_tile) * (n_features / 128u);
+    out->ctas = out->tiles < sm_count ? out->tiles : sm_count;
+    out->tiles_per_cta_max = (out->tiles + out->ctas - 1) / out->ctas;
+    return true;
+}
+
 extern "C" bool q3_cuda_q4k_linear_status(void *stream, uint32_t *status, char *error,
                                           size_t error_len) {
     q3_clear_error(error, error_len);

@@ -33,6 +33,13 @@ def bind_geometry(k, n, qtype=Q4_K):
     return g
 
 
+def plan(tokens, n_features, sm_count=148):
+    """q3_q4_linear_plan: the launch shape for a batch (host arithmetic only)."""
+    info = _lib.LinearPlanInfo()
+    _call(_L().q3_q4_linear_plan, tokens, n_features, sm_count, ctypes.byref(info))
+    return info
+
+
 class Q4Linear:
     """Process-wide set-up plus the scratch arena, like the reference runtime's
     mmq arena. One instance per device."""

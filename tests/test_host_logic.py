@@ -174,3 +174,35 @@ def test_decode_work_covers_every_page_once(pkg):
             assert a[2] == b[1]
         assert all(0 < ch[2] - ch[1] <= 64 for ch in chunks)
     assert work[:, 3].tolist() == list(range(len(work)))
+
+
+def test_linear_geometry_and_plan(pkg):
+    """Host side of the Q4_K linear: geometry binding as the reference's binder
+    does it (ref: src/q3_q4_linear.cu:47-91) and the launch shape."""
+    from sera_c_b200 import q4_linear as q4
+    g = q4.bind_geometry(5120, 10240)
+    assert (g.K, g.N, g.M, g.qtype) == (5120, 10240, 0, 12)
+    assert g.weight_bytes == 10240 * 20 * 144
+    assert q4.bind_geometry(5120, 1024, qtype=q4.Q6_K).weight_bytes == 1024 * 20 * 210
+    for args, msg in (((5000, 128), "multiple of 256"), ((0, 128), "degenerate"),
+                      ((256, 0), "degenerate")):
+        with pytest.raises(pkg.Q3Error, match=msg):
+            q4.bind_geometry(*args)
+    with pytest.raises(pkg.Q3Error, match="neither Q4_K nor Q6_K"):
+        q4.bind_geometry(256, 128, qtype=2)
+    # small batches: one token tile, rounded up to 16
+    for m, want in ((1, 16), (16, 16), (17, 32), (100, 112), (256, 256)):
+        p = q4.plan(m, 10240)
+        assert p.token_tile == want and p.tiles == 80 and p.ctas == 80
+    # large batches: a multiple of 16 in [96, 256] that keeps the last wave full
+    for m, n in ((2048, 10240), (4096, 10240), (2048, 5120), (300, 256), (100000, 1024)):
+        p = q4.plan(m, n)
+        assert p.token_tile % 16 == 0 and 96 <= p.token_tile <= 256
+        assert p.tiles == -(-m // p.token_tile) * (n // 128)
+        assert p.ctas == min(p.tiles, 148)
+        # never worse than the plain 256-token tiling under the same cost model
+        base = -(-(-(-m // 256) * (n // 128)) // 148) * (256 + 32)
+        assert p.tiles_per_cta_max * (p.token_tile + 32) <= base
+    assert q4.plan(2048, 5120).token_tile == 192       # 440 tiles = 2.97 waves
+    with pytest.raises(pkg.Q3Error, match="invalid argument"):
+        q4.plan(16, 100)
