@@ -480,8 +480,19 @@ def random_q4k_weight(torch, n_features, k, device, seed=0):
     return w.view(n_features, -1)
 
 
+def random_q6k_weight(torch, n_features, k, device, seed=0):
+    """Synthetic Q6_K weight [n_features][k/256 blocks of 210 bytes]; d (the f16
+    at the end of each block) drawn so that the weights are O(0.1)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    nb = n_features * (k // 256)
+    w = torch.randint(0, 256, (nb, 210), generator=g, device=device, dtype=torch.uint8)
+    d = (torch.rand(nb, generator=g, device=device) * 0.002 + 0.0002).to(torch.float16)
+    w[:, 208:210] = d.view(torch.uint8).view(nb, 2)
+    return w.view(n_features, -1)
+
+
 def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, reps=20,
-                    tiled=True):
+                    tiled=True, qtype=12):
     """Resident Q4_K projection next to the attention path (q/k/v projection of
     Qwen3-32B as one [10240, 5120] weight, or the output projection
     [5120, 8192]): f16 activations in, bf16 out, one kernel. Six weight copies
@@ -489,9 +500,10 @@ def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, rep
     from sera_c_b200 import q4_linear
     peaks = measured_peaks()
     lin = q4_linear.Q4Linear(device.index, M, N, K)
-    geo = q4_linear.bind_geometry(K, N)
+    geo = q4_linear.bind_geometry(K, N, qtype=qtype)
     copies = max(2, int(200e6 // geo.weight_bytes) + 1)
-    ws = [random_q4k_weight(torch, N, K, device, seed=i) for i in range(copies)]
+    make = random_q4k_weight if qtype == 12 else random_q6k_weight
+    ws = [make(torch, N, K, device, seed=i) for i in range(copies)]
     if tiled:   # one-time re-layout (q3_cuda_q4k_linear_pack), not timed
         packed = [lin.pack(geo, w) for w in ws]
         ws, geo = [t for t, _ in packed], packed[0][1]
@@ -522,6 +534,8 @@ CASES.update({
     "q4k_qkv_4096": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 4096, reps=reps),
     "q4k_oproj_2048": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 2048, 5120, 8192, reps),
     "q4k_qkv_16": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 16, reps=reps),
+    "q6k_v_4096": lambda pkg, torch, dev, reps: case_q4k_linear(
+        pkg, torch, dev, 4096, 1024, 5120, reps, qtype=14),
     "q4k_qkv_4096_gguf_layout": lambda pkg, torch, dev, reps: case_q4k_linear(
         pkg, torch, dev, 4096, reps=reps, tiled=False),
 })

@@ -29,8 +29,9 @@
 extern "C" {
 #endif
 
-/* GGML type ids of the weights (ref: src/q3_quant.h:19-22). Only Q4_K is
- * implemented here; Q6_K is refused with an error. */
+/* GGML type ids of the weights (ref: src/q3_quant.h:19-22). Q4_K runs from
+ * the GGUF block order or from the tiled order of q3_cuda_q4k_linear_pack; Q6_K
+ * (210-byte blocks, which TMA cannot fetch) only from the tiled order. */
 enum { Q3_QUANT_Q4_K = 12, Q3_QUANT_Q6_K = 14 };
 #define Q3_QUANT_QK_K 256
 #define Q3_QUANT_Q4_K_BLOCK_BYTES 144
@@ -90,14 +91,18 @@ void q3_cuda_q4k_linear_read_stats(q3_q4_linear_stats *stats, void *stream);
 
 enum { Q3_OUT_F32 = 0, Q3_OUT_BF16 = 1, Q3_OUT_F16 = 2 };
 
-/* One-time re-layout of a resident Q4_K weight (same bytes, same size): the
- * 128 blocks that one 128-feature tile needs for one 256-wide k range are
- * stored back to back (18432 contiguous bytes), tile by tile, so that the
- * kernel fetches them with one dense TMA box instead of 128 strided 144-byte
- * rows. `tiled_geometry` receives the geometry to pass with the tiled copy
- * (qtype Q3_QUANT_Q4_K_TILED); both linear entry points accept either layout.
- * The source may be freed afterwards. */
+/* One-time re-layout of a resident Q4_K or Q6_K weight: the 128 blocks that one
+ * 128-feature tile needs for one 256-wide k range are stored back to back
+ * (Q4_K: 128 x 144 = 18432 contiguous bytes; Q6_K: each 210-byte block padded
+ * to 224, 28672 bytes), tile by tile, so that the kernel fetches them with one
+ * dense TMA box. `tiled` must hold q3_q4_linear_packed_bytes(geometry) bytes;
+ * `tiled_geometry` receives the geometry to pass with the tiled copy (qtype
+ * Q3_QUANT_Q4_K_TILED / Q3_QUANT_Q6_K_TILED). Both linear entry points accept
+ * Q4_K in either order and Q6_K in the tiled order only. The source may be
+ * freed afterwards. */
 #define Q3_QUANT_Q4_K_TILED (12u | (1u << 16))
+#define Q3_QUANT_Q6_K_TILED (14u | (1u << 16))
+size_t q3_q4_linear_packed_bytes(const q3_q4_linear_geometry *geometry);
 bool q3_cuda_q4k_linear_pack(const q3_q4_linear_geometry *geometry, const void *weight,
                              void *tiled, q3_q4_linear_geometry *tiled_geometry,
                              void *stream, char *error, size_t error_len);

@@ -156,6 +156,41 @@ def q6k_dequantize(blocks):
     return out.reshape(-1)
 
 
+def q6k_dequantize_f16_operands(blocks):
+    """The rounding the tensor-core kernel applies to a Q6_K block: per 16
+    elements scale = f16(d * sc), element = f16((q - 32) * scale)."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1, Q6_K_BLOCK_BYTES)
+    exact_q = np.empty((b.shape[0], 2, 128), np.float64)
+    n = b.shape[0]
+    ql = b[:, 0:128].reshape(n, 2, 64).astype(np.int32)
+    qh = b[:, 128:192].reshape(n, 2, 32).astype(np.int32)
+    sc = b[:, 192:208].copy().view(np.int8).reshape(n, 2, 8).astype(np.float32)
+    d = b[:, 208:210].copy().view(np.float16).astype(np.float32)[:, 0]
+    is_ = np.arange(32) // 16
+    out = np.empty((n, 2, 128), np.float16)
+    for q, (lo, shift_q, nib_hi, sc_off) in enumerate(
+            [(0, 0, False, 0), (32, 2, False, 2), (0, 4, True, 4), (32, 6, True, 6)]):
+        low = ql[:, :, lo:lo + 32]
+        low = (low >> 4) if nib_hi else (low & 0xF)
+        val = ((low | (((qh >> shift_q) & 3) << 4)) - 32).astype(np.float64)
+        scale = (d[:, None, None] * sc[:, :, is_ + sc_off]).astype(np.float16).astype(np.float64)
+        out[:, :, 32 * q:32 * q + 32] = (scale * val).astype(np.float16)
+    return out.reshape(-1)
+
+
+def quant_linear(weight_bytes, qtype, x, operands="fp32"):
+    """out[token][feature] in double for a Q4_K or Q6_K weight [features, row bytes];
+    operands as in q4k_linear."""
+    n = weight_bytes.shape[0]
+    if operands == "fp32":
+        f = q4k_dequantize if qtype == Q4_K_TYPE else q6k_dequantize
+        xx = np.asarray(x, np.float32).astype(np.float64)
+    else:
+        f = q4k_dequantize_f16_operands if qtype == Q4_K_TYPE else q6k_dequantize_f16_operands
+        xx = np.asarray(x, np.float32).astype(np.float16).astype(np.float64)
+    return xx @ f(weight_bytes).reshape(n, -1).astype(np.float64).T
+
+
 def q6k_random_blocks(rng, n_blocks, d_max=0.002):
     b = rng.integers(0, 256, (n_blocks, Q6_K_BLOCK_BYTES), dtype=np.uint8)
     d = (rng.random(n_blocks) * d_max + d_max * 0.1).astype(np.float16)

@@ -58,6 +58,7 @@ def bind_linear(L):
     sig("q3_cuda_q4k_linear_read_stats", None, [sp, vp])
     sig("q3_cuda_q4k_linear_f16", b, [gp, vp, vp, sz, vp, u32, vp] + err)
     sig("q3_q4_linear_plan", b, [u32, u32, u32, ctypes.POINTER(LinearPlanInfo)] + err)
+    sig("q3_q4_linear_packed_bytes", sz, [gp])
     sig("q3_cuda_q4k_linear_pack", b, [gp, vp, vp, gp, vp] + err)
     sig("q3_cuda_q4k_linear_status", b, [vp, ctypes.POINTER(u32)] + err)
     # include/q3_lmhead.h

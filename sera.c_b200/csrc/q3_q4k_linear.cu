@@ -46,10 +46,13 @@
 namespace {
 using namespace q3ptx;
 
-constexpr uint32_t kRawRowBytes = Q3_QUANT_Q4_K_BLOCK_BYTES;
-constexpr uint32_t kRawBytes = 128 * kRawRowBytes; /* 128 feature rows, one block each */
+/* Per weight format: bytes of one block as it sits in shared memory. Q6_K
+ * blocks are 210 bytes (not a multiple of 16, so TMA cannot fetch them from
+ * the GGUF order); they exist only in the tiled layout, padded to 224. */
+template <uint32_t QT> struct Fmt;
+template <> struct Fmt<4> { static constexpr uint32_t kRowBytes = 144; };
+template <> struct Fmt<6> { static constexpr uint32_t kRowBytes = 224; };
 constexpr uint32_t kRawStages = 2;
-constexpr uint32_t kTiledRows = kRawBytes / 256;   /* tiled layout: a chunk = 72 rows of 256 B */
 constexpr uint32_t kMaxTokens = 256;               /* token tile = MMA N */
 constexpr uint32_t kXStageBytes = kMaxTokens * 128; /* [256 tokens][64 k] f16 */
 constexpr uint32_t kXStages = 5;
@@ -61,8 +64,15 @@ constexpr uint32_t kColA = 256;                    /* A stage: 128 lanes x 32 co
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSmemX = 0;
 constexpr uint32_t kSmemRaw = kSmemX + kXStages * kXStageBytes;
-constexpr uint32_t kSmemMisc = kSmemRaw + kRawStages * kRawBytes;
-constexpr uint32_t kSmemTotal = kSmemMisc + 256 + 1024; /* + alignment slack */
+template <uint32_t QT>
+struct Smem {
+    static constexpr uint32_t kRowBytes = Fmt<QT>::kRowBytes;
+    static constexpr uint32_t kRawBytes = 128 * kRowBytes;   /* 128 feature rows, one block each */
+    static constexpr uint32_t kTiledRows = kRawBytes / 256;  /* tiled layout: a chunk in rows of 256 B */
+    static constexpr uint32_t kMisc = kSmemRaw + kRawStages * kRawBytes;
+    static constexpr uint32_t kTotal = kMisc + 256 + 1024;   /* + alignment slack */
+};
+static_assert(Smem<6>::kTotal <= 227 * 1024, "shared memory budget");
 static_assert(kColA + kAStages * 32 <= kTmemCols, "tensor memory budget");
 static_assert(kAStages % kGroups == 0, "a group must come back to its own stages");
 
@@ -113,6 +123,104 @@ __device__ __forceinline__ uint32_t dequant_hi(uint32_t pair, __half2 scale,
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+/* One k-step (64 elements) of one Q4_K block -> 32 packed f16 pairs, element
+ * order. j = 32-byte quant group of the block (ref: src/q3_quant.c:44-76). */
+__device__ __forceinline__ void convert_q4(const uint8_t *blk, uint32_t j, uint32_t *v) {
+    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+    const float dd = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+    const float dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    /* sub-blocks 2j (low nibbles) and 2j+1 (high nibbles); scales bytes
+     * 0-3 = hdr.y, 4-7 = hdr.z, 8-11 = hdr.w */
+    const uint32_t bsh = (j & 1u) * 16u;
+    uint32_t sc_lo, mn_lo, sc_hi, mn_hi;
+    if (j < 2) {
+        const uint32_t a = hdr.y >> bsh, b = hdr.z >> bsh;
+        sc_lo = a & 63u;
+        mn_lo = b & 63u;
+        sc_hi = (a >> 8) & 63u;
+        mn_hi = (b >> 8) & 63u;
+    } else {
+        const uint32_t a = hdr.y >> bsh, b = hdr.z >> bsh, c = hdr.w >> bsh;
+        sc_lo = (c & 0xFu) | (((a & 0xffu) >> 6) << 4);
+        mn_lo = ((c & 0xffu) >> 4) | (((b & 0xffu) >> 6) << 4);
+        sc_hi = ((c >> 8) & 0xFu) | ((((a >> 8) & 0xffu) >> 6) << 4);
+        mn_hi = (((c >> 8) & 0xffu) >> 4) | ((((b >> 8) & 0xffu) >> 6) << 4);
+    }
+    const __half2 scale_lo = __float2half2_rn(dd * (float)sc_lo);
+    const __half2 scale_hi = __float2half2_rn(dd * (float)sc_hi);
+    const __half2 noff_lo = __hneg2(__float2half2_rn(dm * (float)mn_lo));
+    const __half2 noff_hi = __hneg2(__float2half2_rn(dm * (float)mn_hi));
+    const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16u + 32u * j);
+    const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32u + 32u * j);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    /* register i = elements (2i, 2i+1) of the k-step: low nibbles of the 32
+     * quant bytes are elements 0..31, high nibbles elements 32..63 */
+#pragma unroll
+    for (uint32_t u = 0; u < 8; u++) {
+        const uint32_t p01 = __byte_perm(w[u], 0u, 0x4140);
+        const uint32_t p23 = __byte_perm(w[u], 0u, 0x4342);
+        v[2 * u] = dequant_lo(p01, scale_lo, noff_lo);
+        v[2 * u + 1] = dequant_lo(p23, scale_lo, noff_lo);
+        v[16 + 2 * u] = dequant_hi(p01, scale_hi, noff_hi);
+        v[16 + 2 * u + 1] = dequant_hi(p23, scale_hi, noff_hi);
+    }
+}
+
+/* Q6_K: `nib` holds two quant bytes in its 16-bit lanes already shifted so that
+ * the wanted nibble is in bits 0-3, `hb4` the two high-bit bytes shifted so that
+ * the wanted 2 bits are in bits 4-5. 0x6400 | q is the f16 1024 + q; the value
+ * is f16((q - 32) * scale). */
+__device__ __forceinline__ uint32_t dequant6(uint32_t nib, uint32_t hb4, __half2 scale) {
+    uint32_t b = (nib & 0x000F000Fu) | (hb4 & 0x00300030u) | 0x64006400u;
+    const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6420)); /* 1056 */
+    __half2 h = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&b), bias), scale);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+/* One k-step (64 elements) of one Q6_K block (ql[128] | qh[64] | scales[16] int8
+ * | d, ref: src/q3_quant.c:78-103). k-step j lies in half h = j / 2 of the block;
+ * its first 32 elements take the nibbles of ql[64h + l], its last 32 those of
+ * ql[64h + 32 + l] (low nibbles for even j, high for odd), both with 2 more bits
+ * from qh[32h + l]; one int8 scale per 16 elements. */
+__device__ __forceinline__ void convert_q6(const uint8_t *blk, uint32_t j, uint32_t *v) {
+    const uint32_t h = j >> 1, odd = j & 1u;
+    const float d = __half2float(
+        __ushort_as_half(*reinterpret_cast<const unsigned short *>(blk + 208)));
+    const uint32_t sc4 = *reinterpret_cast<const uint32_t *>(blk + 192u + 8u * h + 4u * odd);
+    const __half2 s_a0 = __float2half2_rn(d * (float)(int8_t)(sc4 & 0xffu));
+    const __half2 s_a1 = __float2half2_rn(d * (float)(int8_t)((sc4 >> 8) & 0xffu));
+    const __half2 s_b0 = __float2half2_rn(d * (float)(int8_t)((sc4 >> 16) & 0xffu));
+    const __half2 s_b1 = __float2half2_rn(d * (float)(int8_t)(sc4 >> 24));
+    const uint4 *ql = reinterpret_cast<const uint4 *>(blk + 64u * h);
+    const uint4 *qh = reinterpret_cast<const uint4 *>(blk + 128u + 32u * h);
+    const uint32_t nsh = 4u * odd;          /* nibble select */
+    const uint32_t sh_a = 4u * odd;         /* high bits of the first 32 elements */
+    const uint32_t sh_b = 4u * odd + 2u;    /* ... of the last 32 */
+#pragma unroll
+    for (uint32_t c = 0; c < 2; c++) {
+        const uint4 a4 = ql[c], b4 = ql[2 + c], h4 = qh[c];
+        const uint32_t wa[4] = {a4.x, a4.y, a4.z, a4.w};
+        const uint32_t wb[4] = {b4.x, b4.y, b4.z, b4.w};
+        const uint32_t wh[4] = {h4.x, h4.y, h4.z, h4.w};
+        const __half2 sa = c == 0 ? s_a0 : s_a1;
+        const __half2 sb = c == 0 ? s_b0 : s_b1;
+#pragma unroll
+        for (uint32_t i = 0; i < 4; i++) {
+            const uint32_t u = 4 * c + i;   /* quant bytes 4u .. 4u+3 */
+            const uint32_t a01 = __byte_perm(wa[i], 0u, 0x4140) >> nsh;
+            const uint32_t a23 = __byte_perm(wa[i], 0u, 0x4342) >> nsh;
+            const uint32_t b01 = __byte_perm(wb[i], 0u, 0x4140) >> nsh;
+            const uint32_t b23 = __byte_perm(wb[i], 0u, 0x4342) >> nsh;
+            const uint32_t h01 = __byte_perm(wh[i], 0u, 0x4140) << 4;
+            const uint32_t h23 = __byte_perm(wh[i], 0u, 0x4342) << 4;
+            v[2 * u] = dequant6(a01, h01 >> sh_a, sa);
+            v[2 * u + 1] = dequant6(a23, h23 >> sh_a, sa);
+            v[16 + 2 * u] = dequant6(b01, h01 >> sh_b, sb);
+            v[16 + 2 * u + 1] = dequant6(b23, h23 >> sh_b, sb);
+        }
+    }
+}
+
 /* One output row segment: 32 token columns of one feature (lane) - the 32 lanes
  * of a warp store 32 consecutive features of one token per instruction. */
 __device__ __forceinline__ void store_chunk(const LinearParams &p, const uint32_t *v,
@@ -141,12 +249,16 @@ __device__ __forceinline__ void store_chunk(const LinearParams &p, const uint32_
  * waits until every thread has read the previous tile's D out of tensor
  * memory (d_free). A group reads D after it has already converted its next two
  * k-steps, so the MMA has operands to go on with while the rows are stored. */
+template <uint32_t QT>
 __global__ void __launch_bounds__(kThreads, 1)
 q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                      const __grid_constant__ CUtensorMap w_map, const LinearParams p) {
+    constexpr uint32_t kRawRowBytes = Smem<QT>::kRowBytes;
+    constexpr uint32_t kRawBytes = Smem<QT>::kRawBytes;
+    constexpr uint32_t kTiledRows = Smem<QT>::kTiledRows;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    Misc *misc = reinterpret_cast<Misc *>(smem + kSmemMisc);
+    Misc *misc = reinterpret_cast<Misc *>(smem + Smem<QT>::kMisc);
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t n_super = p.K / Q3_QUANT_QK_K;   /* Q4_K blocks per feature row */
@@ -273,8 +385,6 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
         const uint32_t lane_base = ((warp & 3u) * 32u) << 16;
         const uint32_t n_chunks = (p.NT + 31u) / 32u;
         const uint8_t *blk = nullptr;
-        uint4 hdr = make_uint4(0, 0, 0, 0);
-        float dd = 0.f, dm = 0.f;
         uint32_t cur_sb = 0xffffffffu;
         bool alive = true;
 
@@ -337,47 +447,10 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                 if (!alive) break;
                 cur_sb = sb;
                 blk = smem + kSmemRaw + rs * kRawBytes + row * kRawRowBytes;
-                hdr = *reinterpret_cast<const uint4 *>(blk);
-                dd = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
-                dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
             }
-            /* sub-blocks 2j (low nibbles) and 2j+1 (high nibbles); scales bytes
-             * 0-3 = hdr.y, 4-7 = hdr.z, 8-11 = hdr.w */
-            const uint32_t bsh = (j & 1u) * 16u;
-            uint32_t sc_lo, mn_lo, sc_hi, mn_hi;
-            if (j < 2) {
-                const uint32_t a = hdr.y >> bsh, b = hdr.z >> bsh;
-                sc_lo = a & 63u;
-                mn_lo = b & 63u;
-                sc_hi = (a >> 8) & 63u;
-                mn_hi = (b >> 8) & 63u;
-            } else {
-                const uint32_t a = hdr.y >> bsh, b = hdr.z >> bsh, c = hdr.w >> bsh;
-                sc_lo = (c & 0xFu) | (((a & 0xffu) >> 6) << 4);
-                mn_lo = ((c & 0xffu) >> 4) | (((b & 0xffu) >> 6) << 4);
-                sc_hi = ((c >> 8) & 0xFu) | ((((a >> 8) & 0xffu) >> 6) << 4);
-                mn_hi = (((c >> 8) & 0xffu) >> 4) | ((((b >> 8) & 0xffu) >> 6) << 4);
-            }
-            const __half2 scale_lo = __float2half2_rn(dd * (float)sc_lo);
-            const __half2 scale_hi = __float2half2_rn(dd * (float)sc_hi);
-            const __half2 noff_lo = __hneg2(__float2half2_rn(dm * (float)mn_lo));
-            const __half2 noff_hi = __hneg2(__float2half2_rn(dm * (float)mn_hi));
-
-            const uint4 qa = *reinterpret_cast<const uint4 *>(blk + 16u + 32u * j);
-            const uint4 qb = *reinterpret_cast<const uint4 *>(blk + 32u + 32u * j);
-            const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-            /* register i = elements (2i, 2i+1) of the k-step: low nibbles of the
-             * 32 quant bytes are elements 0..31, high nibbles elements 32..63 */
             uint32_t v[32];
-#pragma unroll
-            for (uint32_t u = 0; u < 8; u++) {
-                const uint32_t p01 = __byte_perm(w[u], 0u, 0x4140);
-                const uint32_t p23 = __byte_perm(w[u], 0u, 0x4342);
-                v[2 * u] = dequant_lo(p01, scale_lo, noff_lo);
-                v[2 * u + 1] = dequant_lo(p23, scale_lo, noff_lo);
-                v[16 + 2 * u] = dequant_hi(p01, scale_hi, noff_hi);
-                v[16 + 2 * u + 1] = dequant_hi(p23, scale_hi, noff_hi);
-            }
+            if constexpr (QT == 4) convert_q4(blk, j, v);
+            else convert_q6(blk, j, v);
             /* The store of the previous step has had this step's conversion
              * time to retire: publish it now, then issue this step's store and
              * go on without waiting for it. */
@@ -419,6 +492,22 @@ __global__ void q4k_pack_kernel(const uint4 *__restrict__ src, uint4 *__restrict
     const uint32_t row = (uint32_t)(blk / n_super);
     const size_t chunk = (size_t)(row / 128u) * n_super + sb;
     dst[(chunk * 128u + (row % 128u)) * 9u + part] = src[i];
+}
+
+/* Q6_K: GGUF row-major 210-byte blocks -> tiled chunks of 128 slots of 224 bytes
+ * (block + 14 zero bytes). One thread per block, 2-byte granularity (the source
+ * is only 2-byte aligned). */
+__global__ void q6k_pack_kernel(const uint16_t *__restrict__ src, uint16_t *__restrict__ dst,
+                                uint32_t n_rows, uint32_t n_super) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_rows * n_super) return;
+    const uint32_t sb = (uint32_t)(i % n_super);
+    const uint32_t row = (uint32_t)(i / n_super);
+    const size_t chunk = (size_t)(row / 128u) * n_super + sb;
+    const uint16_t *s = src + i * 105u;
+    uint16_t *d = dst + (chunk * 128u + (row % 128u)) * 112u;
+    for (uint32_t w = 0; w < 105u; w++) d[w] = s[w];
+    for (uint32_t w = 105u; w < 112u; w++) d[w] = 0;
 }
 
 /* fp32 -> f16, 8 elements per thread (n is a multiple of 256: K is). */
@@ -479,9 +568,13 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
                    size_t tokens, void *out, uint32_t out_type, cudaStream_t stream,
                    char *error, size_t error_len) {
     const uint32_t M = (uint32_t)tokens, N = (uint32_t)geo->N, K = (uint32_t)geo->K;
-    if (geo->qtype != Q3_QUANT_Q4_K && geo->qtype != Q3_QUANT_Q4_K_TILED)
+    if (geo->qtype == Q3_QUANT_Q6_K)
         return q3_fail(error, error_len,
-                       "q3_q4_linear: only Q4_K weights are implemented (Q6_K is not)");
+                       "q3_q4_linear: a Q6_K weight must first be re-laid out with "
+                       "q3_cuda_q4k_linear_pack (210-byte blocks cannot be fetched by TMA)");
+    if (geo->qtype != Q3_QUANT_Q4_K && geo->qtype != Q3_QUANT_Q4_K_TILED &&
+        geo->qtype != Q3_QUANT_Q6_K_TILED)
+        return q3_fail(error, error_len, "q3_q4_linear: weight is neither Q4_K nor Q6_K");
     if (K % Q3_QUANT_QK_K || N % 128u)
         return q3_fail(error, error_len,
                        "q3_q4_linear: K must be a multiple of 256 and N of 128");
@@ -497,21 +590,27 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
     p.NT = choose_token_tile(M, N, sms);
     p.out_type = out_type;
     p.status = g.status_dev;
-    p.w_tiled = geo->qtype == Q3_QUANT_Q4_K_TILED ? 1u : 0u;
+    const bool q6 = geo->qtype == Q3_QUANT_Q6_K_TILED;
+    p.w_tiled = geo->qtype != Q3_QUANT_Q4_K ? 1u : 0u;
     CUtensorMap x_map, w_map;
     if (!q3_encode_tmap_2d(&x_map, x_f16, K, M, 64, p.NT, error, error_len)) return false;
-    const uint64_t row_bytes = (uint64_t)(K / Q3_QUANT_QK_K) * kRawRowBytes;
+    const uint32_t slot = q6 ? Smem<6>::kRowBytes : Smem<4>::kRowBytes;
+    const uint64_t row_bytes = (uint64_t)(K / Q3_QUANT_QK_K) * slot;
     if (p.w_tiled) {
-        if (!q3_encode_tmap_bytes_2d(&w_map, weight, 256, row_bytes * N / 256, 256, kTiledRows,
-                                     error, error_len))
+        if (!q3_encode_tmap_bytes_2d(&w_map, weight, 256, row_bytes * N / 256, 256,
+                                     q6 ? Smem<6>::kTiledRows : Smem<4>::kTiledRows, error,
+                                     error_len))
             return false;
-    } else if (!q3_encode_tmap_bytes_2d(&w_map, weight, row_bytes, N, kRawRowBytes, 128, error,
+    } else if (!q3_encode_tmap_bytes_2d(&w_map, weight, row_bytes, N, slot, 128, error,
                                         error_len)) {
         return false;
     }
     const uint32_t n_tiles = ((M + p.NT - 1) / p.NT) * (N / 128);
     const uint32_t grid = n_tiles < (uint32_t)sms ? n_tiles : (uint32_t)sms;
-    q4k_linear_tc_kernel<<<grid, kThreads, kSmemTotal, stream>>>(x_map, w_map, p);
+    if (q6)
+        q4k_linear_tc_kernel<6><<<grid, kThreads, Smem<6>::kTotal, stream>>>(x_map, w_map, p);
+    else
+        q4k_linear_tc_kernel<4><<<grid, kThreads, Smem<4>::kTotal, stream>>>(x_map, w_map, p);
     Q3_LAUNCH_CHECK("q4k_linear_tc launch failed");
     return true;
 }
@@ -561,8 +660,12 @@ extern "C" bool q3_cuda_q4k_linear_init(int device, size_t max_tokens, int64_t m
         return q3_fail(error, error_len, "q3_q4_linear: no CUDA device");
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "q3_q4_linear: cudaSetDevice", e);
-    e = cudaFuncSetAttribute(q4k_linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kSmemTotal);
+    e = cudaFuncSetAttribute(q4k_linear_tc_kernel<4>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<4>::kTotal);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(q4k_linear_tc_kernel<6>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Smem<6>::kTotal);
     if (e == cudaSuccess) e = cudaGetSymbolAddress((void **)&g.status_dev, q3_linear_status_word);
     if (e == cudaSuccess) e = cudaMemset(g.status_dev, 0, sizeof(uint32_t));
     if (e == cudaSuccess && !g.ev_begin) {
@@ -665,6 +768,14 @@ extern "C" bool q3_cuda_q4k_linear_f16(const q3_q4_linear_geometry *geometry,
                          (cudaStream_t)stream, error, error_len);
 }
 
+extern "C" size_t q3_q4_linear_packed_bytes(const q3_q4_linear_geometry *geometry) {
+    if (!geometry || geometry->N <= 0 || geometry->K <= 0) return 0;
+    const size_t blocks = (size_t)geometry->N * ((size_t)geometry->K / Q3_QUANT_QK_K);
+    if (geometry->qtype == Q3_QUANT_Q4_K) return blocks * Smem<4>::kRowBytes;
+    if (geometry->qtype == Q3_QUANT_Q6_K) return blocks * Smem<6>::kRowBytes;
+    return 0;
+}
+
 extern "C" bool q3_cuda_q4k_linear_pack(const q3_q4_linear_geometry *geometry,
                                         const void *weight, void *tiled,
                                         q3_q4_linear_geometry *tiled_geometry, void *stream,
@@ -672,21 +783,31 @@ extern "C" bool q3_cuda_q4k_linear_pack(const q3_q4_linear_geometry *geometry,
     q3_clear_error(error, error_len);
     if (!geometry || !weight || !tiled || !tiled_geometry)
         return q3_fail(error, error_len, "q3_q4_linear: null argument");
-    if (geometry->qtype != Q3_QUANT_Q4_K)
-        return q3_fail(error, error_len, "q3_q4_linear: pack takes a Q4_K weight in GGUF order");
+    if (geometry->qtype != Q3_QUANT_Q4_K && geometry->qtype != Q3_QUANT_Q6_K)
+        return q3_fail(error, error_len,
+                       "q3_q4_linear: pack takes a Q4_K or Q6_K weight in GGUF order");
     if (geometry->N <= 0 || geometry->K <= 0 || geometry->N % 128 || geometry->K % Q3_QUANT_QK_K)
         return q3_fail(error, error_len,
                        "q3_q4_linear: K must be a multiple of 256 and N of 128");
-    if (((uintptr_t)weight | (uintptr_t)tiled) & 15u)
-        return q3_fail(error, error_len, "q3_q4_linear: pointers must be 16-byte aligned");
+    const bool q6 = geometry->qtype == Q3_QUANT_Q6_K;
+    if (((uintptr_t)tiled & 15u) || ((uintptr_t)weight & (q6 ? 1u : 15u)))
+        return q3_fail(error, error_len, "q3_q4_linear: misaligned pointer");
     const uint32_t n_super = (uint32_t)geometry->K / Q3_QUANT_QK_K;
-    const size_t total = (size_t)geometry->N * n_super * 9u;
-    q4k_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        static_cast<const uint4 *>(weight), static_cast<uint4 *>(tiled), (uint32_t)geometry->N,
-        n_super);
+    if (q6) {
+        const size_t total = (size_t)geometry->N * n_super;
+        q6k_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            static_cast<const uint16_t *>(weight), static_cast<uint16_t *>(tiled),
+            (uint32_t)geometry->N, n_super);
+    } else {
+        const size_t total = (size_t)geometry->N * n_super * 9u;
+        q4k_pack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+            static_cast<const uint4 *>(weight), static_cast<uint4 *>(tiled),
+            (uint32_t)geometry->N, n_super);
+    }
     Q3_LAUNCH_CHECK("q3_q4_linear: pack launch failed");
     *tiled_geometry = *geometry;
-    tiled_geometry->qtype = Q3_QUANT_Q4_K_TILED;
+    tiled_geometry->qtype = q6 ? Q3_QUANT_Q6_K_TILED : Q3_QUANT_Q4_K_TILED;
+    tiled_geometry->weight_bytes = q3_q4_linear_packed_bytes(geometry);
     return true;
 }
 

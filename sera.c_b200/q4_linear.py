@@ -78,7 +78,10 @@ class Q4Linear:
 
     def pack(self, geo, weight, stream=None):
         """q3_cuda_q4k_linear_pack: returns (tiled weight, tiled geometry)."""
-        tiled = self.torch.empty_like(weight)
+        nbytes = int(_L().q3_q4_linear_packed_bytes(ctypes.byref(geo)))
+        if nbytes == 0:
+            raise Q3Error("pack takes a Q4_K or Q6_K weight in GGUF order")
+        tiled = self.torch.empty(nbytes, dtype=self.torch.uint8, device=weight.device)
         tg = LinearGeometry()
         _call(_L().q3_cuda_q4k_linear_pack, ctypes.byref(geo), weight.data_ptr(),
               tiled.data_ptr(), ctypes.byref(tg), stream)

@@ -80,6 +80,35 @@ def test_tiled_weight_layout_is_bit_identical(lin, M, N, K):
     assert L.status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(3, 128, 256), (70, 256, 1024), (300, 384, 768),
+                                   (1000, 1024, 5120)])
+def test_q6k_weight_through_the_tiled_layout(lin, M, N, K):
+    """Q6_K (attn_v / ffn_down / output tensors of a Q4_K_M file): packed once
+    into 224-byte slots, then the same kernel with the Q6_K conversion. Parity
+    bars as for Q4_K; the GGUF order itself is refused."""
+    q4, L = lin
+    from sera_c_b200 import Q3Error
+    rng = np.random.default_rng(M + N + K)
+    w = qo.q6k_random_blocks(rng, N * (K // 256)).reshape(N, -1)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    geo = q4.bind_geometry(K, N, qtype=q4.Q6_K)
+    wd = torch.from_numpy(w).cuda()
+    xd = torch.from_numpy(x).cuda().half()
+    with pytest.raises(Q3Error, match="re-laid out"):
+        L.linear_f16(geo, wd, xd)
+    tiled, tgeo = L.pack(geo, wd)
+    assert tgeo.qtype == (14 | (1 << 16)) and tiled.numel() == N * (K // 256) * 224
+    slots = tiled.cpu().numpy().reshape(N // 128, K // 256, 128, 224)
+    want = w.reshape(N // 128, 128, K // 256, 210).transpose(0, 2, 1, 3)
+    assert np.array_equal(slots[..., :210], want) and not slots[..., 210:].any()
+    got = L.linear_f16(tgeo, tiled, xd, out_dtype=torch.float32).cpu().numpy()
+    assert L.status() == 0
+    m16 = qo.linear_error_metrics(got, qo.quant_linear(w, 14, x, operands="f16"))
+    assert m16["rel_l2"] < 1e-4, m16
+    exact = qo.linear_error_metrics(got, qo.quant_linear(w, 14, x))
+    assert exact["rel_l2"] < 1e-3 and exact["cos"] > 0.99999, exact
+
+
 def test_rows_beyond_the_batch_are_untouched(lin):
     q4, L = lin
     w, x = _case(9, 70, 256, 512)
@@ -128,7 +157,7 @@ def test_error_paths(lin):
     geo = q4.bind_geometry(512, 256)
     w = torch.zeros(256 * 2 * 144, dtype=torch.uint8, device="cuda")
     x = torch.zeros(8, 512, dtype=torch.float16, device="cuda")
-    with pytest.raises(Q3Error, match="Q6_K"):
+    with pytest.raises(Q3Error, match="Q6_K weight must first be re-laid out"):
         L.linear_f16(q4.bind_geometry(512, 256, qtype=q4.Q6_K), w, x)
     with pytest.raises(Q3Error, match="N of 128"):
         L.linear_f16(q4.bind_geometry(512, 200), w, x)

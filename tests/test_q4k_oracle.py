@@ -113,3 +113,10 @@ def test_candidate_head_oracle_small():
     deq = qo.q6k_dequantize(w).reshape(6, 512).astype(np.float64)
     assert abs(out[1] - float(deq[5] @ rows[1].astype(np.float64))) < 1e-9
     assert abs(out[2] - float(deq[3] @ rows[4].astype(np.float64))) < 1e-9
+
+
+def test_q6k_f16_operand_model_is_close_to_exact():
+    blocks = qo.q6k_random_blocks(np.random.default_rng(4), 64)
+    exact = qo.q6k_dequantize(blocks).astype(np.float64)
+    f16 = qo.q6k_dequantize_f16_operands(blocks).astype(np.float64)
+    assert np.abs(f16 - exact).max() <= 2e-3 * np.abs(exact).max()
