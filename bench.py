@@ -696,7 +696,6 @@ def reference_gpu_kernels():
     # the reference's Q4_K linear (Q8_1 activation quantisation + MMQ) on the q/k/v shape
     qpath = os.path.join(ROOT, "oracle", "_ref", "libq3q4ref.so")
     if os.path.exists(qpath):
-        sys.path.insert(0, os.path.join(ROOT, "sera.c_b200"))
         import __graft_entry__ as entry
         entry.load_package()
         from sera_c_b200 import _lib
