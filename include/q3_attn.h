@@ -317,6 +317,42 @@ bool q3_attn_wait_gathered(q3_attn_runtime *rt, const q3_gather_peers *gather,
 bool q3_attn_gather_advance(q3_attn_runtime *rt, uint32_t count, char *error,
                             size_t error_len);
 
+/* --- sealed prefixes kept across requests -------------------------------- *
+ * The reference creates, prefills and destroys the prefix once per request
+ * (ref: src/q3_systemone.cu:498-523, 740-741). With pages a sealed prefix is a
+ * page table, so it can outlive the request: the cache keeps sealed prefixes
+ * under a caller-chosen key (e.g. a hash of the prompt's token ids), hands them
+ * out by reference count and evicts the least recently used unreferenced ones;
+ * their pages return to the pool's free list and are reused without any
+ * allocation. Host code only. */
+typedef struct q3_prefix_cache q3_prefix_cache;
+typedef struct {
+    uint64_t hits, misses, inserts, evictions;
+    uint32_t entries;
+    uint32_t pages_held;
+} q3_prefix_cache_stats;
+q3_prefix_cache *q3_prefix_cache_create(q3_attn_runtime *rt, uint32_t max_entries,
+                                        char *error, size_t error_len);
+/* Destroys every prefix it still holds. */
+void q3_prefix_cache_destroy(q3_prefix_cache *cache);
+/* Hit (same key and token count): one more reference, returns the prefix.
+ * Miss: NULL - the caller prefills a new prefix and inserts it. */
+q3_prefix_kv *q3_prefix_cache_acquire(q3_prefix_cache *cache, uint64_t key,
+                                      uint32_t token_count);
+/* Gives a sealed prefix to the cache (the cache destroys it on eviction); the
+ * caller keeps one reference, as after an acquire. At max_entries the least
+ * recently used unreferenced entry is evicted first. */
+bool q3_prefix_cache_insert(q3_prefix_cache *cache, uint64_t key, q3_prefix_kv *prefix,
+                            char *error, size_t error_len);
+bool q3_prefix_cache_release(q3_prefix_cache *cache, q3_prefix_kv *prefix, char *error,
+                             size_t error_len);
+/* Evicts unreferenced entries, least recently used first, until the pool has
+ * `pages_needed` free pages or nothing more can go; returns the number evicted. */
+uint32_t q3_prefix_cache_make_room(q3_prefix_cache *cache, uint32_t pages_needed);
+/* 1 while the cache holds `prefix` (an evicted prefix no longer exists). */
+int q3_prefix_cache_holds(const q3_prefix_cache *cache, const q3_prefix_kv *prefix);
+void q3_prefix_cache_get_stats(const q3_prefix_cache *cache, q3_prefix_cache_stats *out);
+
 /* --- replaying a fixed sequence of layer calls as one CUDA graph --------- *
  * The reference notes CUDA-graph capture of the 64-layer stack as the natural
  * next step of its launch plumbing (ref: docs/M3.md, src/q3_forward.cu:1588-1651

@@ -13,6 +13,7 @@ import os
 
 import numpy as np
 
+from . import _lib
 from ._lib import ERRLEN, GatherPeers, Q3Error, bind, lib_path  # noqa: F401
 
 PAGE = 16
@@ -250,6 +251,51 @@ class Prefix:
         n = (self.capacity + PAGE - 1) // PAGE
         p = lib().q3_prefix_page_table(self.h)
         return np.ctypeslib.as_array(p, shape=(n,)).copy()
+
+
+class PrefixCache:
+    """q3_prefix_cache: sealed prefixes kept across requests, by key."""
+
+    def __init__(self, rt, max_entries):
+        self.rt = rt
+        self.h = _call(lib().q3_prefix_cache_create, rt.h, max_entries)
+        self._by_handle = {}
+
+    def acquire(self, key, token_count):
+        h = lib().q3_prefix_cache_acquire(self.h, key, token_count)
+        return self._by_handle.get(h) if h else None
+
+    def insert(self, key, prefix):
+        _call(lib().q3_prefix_cache_insert, self.h, key, prefix.h)
+        self._by_handle[prefix.h] = prefix     # the cache owns the handle from here on
+
+    def release(self, prefix):
+        _call(lib().q3_prefix_cache_release, self.h, prefix.h)
+
+    def make_room(self, pages_needed):
+        n = lib().q3_prefix_cache_make_room(self.h, pages_needed)
+        self._forget_evicted()
+        return n
+
+    def stats(self):
+        st = _lib.PrefixCacheStats()
+        lib().q3_prefix_cache_get_stats(self.h, ctypes.byref(st))
+        return st
+
+    def _forget_evicted(self):
+        # handles the library destroyed must not be destroyed again from Python
+        live = self.stats().entries
+        if live < len(self._by_handle):
+            for h in list(self._by_handle):
+                if lib().q3_prefix_cache_holds(self.h, h) == 0:
+                    self._by_handle.pop(h).h = None
+
+    def close(self):
+        if getattr(self, "h", None):
+            for p in self._by_handle.values():
+                p.h = None
+            lib().q3_prefix_cache_destroy(self.h)
+            self.h = None
 
 
 class BranchSet:

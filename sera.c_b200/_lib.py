@@ -70,6 +70,13 @@ def bind_linear(L):
     return L
 
 
+class PrefixCacheStats(ctypes.Structure):
+    """q3_prefix_cache_stats"""
+    _fields_ = [("hits", ctypes.c_uint64), ("misses", ctypes.c_uint64),
+                ("inserts", ctypes.c_uint64), ("evictions", ctypes.c_uint64),
+                ("entries", ctypes.c_uint32), ("pages_held", ctypes.c_uint32)]
+
+
 class GatherPeers(ctypes.Structure):
     _fields_ = [("n_ranks", ctypes.c_uint32), ("rank", ctypes.c_uint32),
                 ("gathered", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8)]
@@ -166,6 +173,14 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
         [vp, u32, vp, vp, vp, ctypes.POINTER(GatherPeers), u32] + err)
     sig("q3_attn_wait_gathered", b, [vp, ctypes.POINTER(GatherPeers), u32] + err)
     sig("q3_attn_gather_advance", b, [vp, u32] + err)
+    sig("q3_prefix_cache_create", vp, [vp, u32] + err)
+    sig("q3_prefix_cache_destroy", None, [vp])
+    sig("q3_prefix_cache_acquire", vp, [vp, u64, u32])
+    sig("q3_prefix_cache_insert", b, [vp, u64, vp] + err)
+    sig("q3_prefix_cache_release", b, [vp, vp] + err)
+    sig("q3_prefix_cache_make_room", u32, [vp, u32])
+    sig("q3_prefix_cache_holds", ctypes.c_int, [vp, vp])
+    sig("q3_prefix_cache_get_stats", None, [vp, ctypes.POINTER(PrefixCacheStats)])
     sig("q3_attn_graph_begin", b, [vp] + err)
     sig("q3_attn_graph_end", vp, [vp] + err)
     sig("q3_attn_graph_launch", b, [vp] + err)

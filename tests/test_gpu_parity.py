@@ -445,3 +445,72 @@ def test_cascade_8192_sampled_rows(pkg):
     for o in (plan, bset, prefix):
         o.close()
     rt.close()
+
+
+def test_prefix_cache_across_requests(pkg):
+    """q3_prefix_cache: a sealed prefix outlives its request; the second request
+    with the same key skips the prefill and gets identical rows; under pressure
+    the least recently used unreferenced prefix is evicted and its pages are
+    reused without any allocation."""
+    case = harness.rounded_case(_cases.make_case("ragged"))
+    P, S = case.P, case.S
+    pages = (P + 15) // 16
+    # the prefix must own its pages (taken from the pool's free list) to give them back
+    _, rt, prefix, bset, plan = harness.run_case_native(pkg, case, return_runtime=True,
+                                                        permute_pages=False)
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(S, case.H, case.D, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(S, case.Hkv, case.D, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(S, case.Hkv, case.D, generator=g).to(torch.bfloat16).cuda()
+    first = torch.zeros(S, case.H, case.D, dtype=torch.bfloat16, device="cuda")
+    plan.attention_layer(1, q, k, v, first)
+    rt.synchronize()
+    cache = pkg.PrefixCache(rt, max_entries=2)
+    with pytest.raises(pkg.Q3Error, match="null argument"):
+        pkg._call(pkg.lib().q3_prefix_cache_insert, cache.h, 1, None)
+    cache.insert(0xABCD, prefix)                      # request 1 hands its prefix over
+    with pytest.raises(pkg.Q3Error, match="already cached"):
+        cache.insert(0xABCD, prefix)
+    cache.release(prefix)
+    for o in (plan, bset):
+        o.close()
+
+    # request 2: same prompt -> hit, no prefill, same rows
+    hit = cache.acquire(0xABCD, P)
+    assert hit is prefix and cache.acquire(0xABCD, P + 1) is None and cache.acquire(7, P) is None
+    bset2 = pkg.BranchSet(hit, len(case.branch_lens), max(case.branch_lens))
+    handles = [bset2.acquire() for _ in case.branch_lens]
+    plan2 = pkg.PackPlan(hit, bset2, list(zip(handles, case.branch_lens)))
+    second = torch.zeros_like(first)
+    plan2.attention_layer(1, q, k, v, second)
+    rt.synchronize()
+    assert torch.equal(first, second)
+    for o in (plan2, bset2):
+        o.close()
+    st = cache.stats()
+    assert (st.hits, st.misses, st.inserts, st.evictions, st.entries) == (1, 2, 1, 0, 1)
+    assert st.pages_held == pages
+
+    # a referenced prefix is never evicted; once released it goes when room is needed
+    free0 = rt.stats().pages_free
+    assert cache.make_room(free0 + 1) == 0 and cache.stats().entries == 1
+    cache.release(hit)
+    other = pkg.Prefix(rt, 40)
+    other.set_resident(40)
+    other.seal()
+    cache.insert(2, other)
+    cache.release(other)
+    assert cache.acquire(2, 40) is other               # `other` is now the most recent
+    cache.release(other)
+    assert cache.make_room(rt.stats().pages_free + 1) == 1          # evicts 0xABCD (LRU)
+    assert prefix.h is None and cache.acquire(0xABCD, P) is None
+    assert rt.stats().pages_free == free0 - 3 + pages
+    allocs = rt.stats().cuda_allocations
+    reuse = pkg.Prefix(rt, P)                          # takes the freed pages from the list
+    assert rt.stats().cuda_allocations == allocs
+    assert set(reuse.page_table().tolist()) & set(range(rt.stats().pages_total))
+    reuse.close()
+    st = cache.stats()
+    assert (st.evictions, st.entries, st.pages_held) == (1, 1, 3)
+    cache.close()
+    rt.close()
