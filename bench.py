@@ -526,14 +526,22 @@ def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, rep
             "tokens_per_s": M / (ms * 1e-3), "M": M, "N": N, "K": K,
             "weight_bytes": int(geo.weight_bytes), "status": lin.status(),
             "weight_layout": "tiled (packed once)" if tiled else "GGUF row-major",
-            "algorithmic_bytes": int(geo.weight_bytes + M * K * 2 + M * N * 2)}
+            "algorithmic_bytes": int(geo.weight_bytes + M * K * 2 + M * N * 2),
+            "gbs": (geo.weight_bytes + M * K * 2 + M * N * 2) / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": (geo.weight_bytes + M * K * 2 + M * N * 2) / (ms * 1e-3) / 1e9
+                                / peaks["hbm_gbs"]}
 
 
 CASES.update({
     "q4k_qkv_2048": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 2048, reps=reps),
     "q4k_qkv_4096": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 4096, reps=reps),
     "q4k_oproj_2048": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 2048, 5120, 8192, reps),
-    "q4k_qkv_16": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 16, reps=reps),
+    "q4k_qkv_16": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 16, reps=reps,
+                                                               tiled=False),
+    "q4k_qkv_1": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 1, reps=reps,
+                                                              tiled=False),
+    "q4k_qkv_16_tile_kernel": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 16,
+                                                                           reps=reps),
     "q6k_v_4096": lambda pkg, torch, dev, reps: case_q4k_linear(
         pkg, torch, dev, 4096, 1024, 5120, reps, qtype=14),
     "q4k_qkv_4096_gguf_layout": lambda pkg, torch, dev, reps: case_q4k_linear(

@@ -76,7 +76,9 @@ bool q3_cuda_q4k_linear_init(int device, size_t max_tokens, int64_t max_features
 size_t q3_cuda_q4k_linear_workspace_bytes(void);
 bool q3_cuda_q4k_linear_set_workspace(void *device_ptr, size_t bytes, char *error,
                                       size_t error_len);
-/* The reference answers "MMVQ" or "MMQ"; this library has one path, "TC". */
+/* The reference answers "MMVQ" or "MMQ"; this library answers "MMA-small" (at
+ * most 16 tokens, Q4_K in GGUF order: an mma.sync kernel without the tile pipeline)
+ * or "TC" (the tcgen05 tile kernel). */
 const char *q3_cuda_q4k_linear_path_for_batch(size_t token_count);
 
 /* Q4_K weight x fp32 activation -> fp32 output (ref: src/q3_q4_linear.h:93-108). */

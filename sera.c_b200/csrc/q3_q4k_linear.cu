@@ -43,6 +43,12 @@
 #include "q3_ptx.cuh"
 #include "q3_q4_linear.h"
 
+/* q3_q4k_small.cu */
+#define Q3_Q4K_SMALL_BATCH 16u
+bool q3_launch_q4k_small(const void *weight, const void *x_f16, uint32_t M, uint32_t N,
+                         uint32_t K, void *out, uint32_t out_type, cudaStream_t stream,
+                         char *error, size_t error_len);
+
 namespace {
 using namespace q3ptx;
 
@@ -580,6 +586,9 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
                        "q3_q4_linear: K must be a multiple of 256 and N of 128");
     if (((uintptr_t)weight | (uintptr_t)x_f16 | (uintptr_t)out) & 15u)
         return q3_fail(error, error_len, "q3_q4_linear: pointers must be 16-byte aligned");
+    if (geo->qtype == Q3_QUANT_Q4_K && M <= Q3_Q4K_SMALL_BATCH)
+        return q3_launch_q4k_small(weight, x_f16, M, N, K, out, out_type, stream, error,
+                                   error_len);
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g.device);
     LinearParams p;
@@ -699,8 +708,7 @@ extern "C" bool q3_cuda_q4k_linear_set_workspace(void *device_ptr, size_t bytes,
 }
 
 extern "C" const char *q3_cuda_q4k_linear_path_for_batch(size_t token_count) {
-    (void)token_count;
-    return "TC";
+    return token_count <= Q3_Q4K_SMALL_BATCH ? "MMA-small" : "TC";
 }
 
 extern "C" bool q3_cuda_q4k_linear(const q3_q4_linear_geometry *geometry, const void *weight,

@@ -37,6 +37,7 @@ def _case(seed, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 256), (4, 256, 512), (16, 128, 1024),
+                                   (17, 256, 768), (32, 1024, 5120), (33, 128, 512),
                                    (100, 384, 768), (128, 128, 256), (129, 256, 512),
                                    (300, 256, 1280), (513, 1024, 5120)])
 def test_f16_entry_matches_oracle(lin, M, N, K):
@@ -58,7 +59,7 @@ def test_f16_entry_matches_oracle(lin, M, N, K):
             assert exact["rel_l2"] < 1e-3 and exact["cos"] > 0.99999, exact
 
 
-@pytest.mark.parametrize("M,N,K", [(5, 128, 256), (200, 384, 1024), (700, 1024, 2560)])
+@pytest.mark.parametrize("M,N,K", [(20, 128, 256), (200, 384, 1024), (700, 1024, 2560)])
 def test_tiled_weight_layout_is_bit_identical(lin, M, N, K):
     """q3_cuda_q4k_linear_pack: same bytes regrouped per (feature tile, 256-wide
     k range); the linear gives bit-identical output from either layout, and the
@@ -107,6 +108,25 @@ def test_q6k_weight_through_the_tiled_layout(lin, M, N, K):
     assert m16["rel_l2"] < 1e-4, m16
     exact = qo.linear_error_metrics(got, qo.quant_linear(w, 14, x))
     assert exact["rel_l2"] < 1e-3 and exact["cos"] > 0.99999, exact
+
+
+def test_small_batch_path_matches_tile_kernel(lin):
+    """At most 16 tokens take the mma.sync kernel (GGUF order); the same batch
+    through the tiled order takes the tcgen05 kernel. Same operands, different
+    summation order: equal to 1e-5 relative L2."""
+    q4, L = lin
+    assert q4._L().q3_cuda_q4k_linear_path_for_batch(8) == b"MMA-small"
+    assert q4._L().q3_cuda_q4k_linear_path_for_batch(17) == b"TC"
+    w, x = _case(77, 13, 512, 2048)
+    geo = q4.bind_geometry(2048, 512)
+    wd = torch.from_numpy(w).cuda()
+    xd = torch.from_numpy(x).cuda().half()
+    tiled, tgeo = L.pack(geo, wd)
+    a = L.linear_f16(geo, wd, xd, out_dtype=torch.float32).cpu().numpy()
+    b = L.linear_f16(tgeo, tiled, xd, out_dtype=torch.float32).cpu().numpy()
+    m = qo.linear_error_metrics(a, b)
+    assert m["rel_l2"] < 1e-5, m
+    assert L.status() == 0
 
 
 def test_rows_beyond_the_batch_are_untouched(lin):
