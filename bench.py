@@ -549,6 +549,46 @@ CASES.update({
 })
 
 
+def case_q4k_mmvq(pkg, torch, device, M=1, N=(H + 2 * HKV) * D, K=5120, reps=50):
+    """The fp32 reference surface (q3_cuda_q4k_linear) on a decode-size batch: the
+    reference's 8-bit-activation arithmetic, bound by the weight bytes."""
+    from sera_c_b200 import q4_linear
+    peaks = measured_peaks()
+    lin = q4_linear.Q4Linear(device.index, max(M, 16), N, K)
+    geo = q4_linear.bind_geometry(K, N)
+    copies = max(2, int(200e6 // geo.weight_bytes) + 1)
+    ws = [random_q4k_weight(torch, N, K, device, seed=i) for i in range(copies)]
+    g = torch.Generator(device=device).manual_seed(1)
+    x = torch.randn(M, K, generator=g, device=device)
+    out = torch.empty(M, N, dtype=torch.float32, device=device)
+    for i in range(3):
+        lin.linear_f32(geo, ws[i % copies], x, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        lin.linear_f32(geo, ws[i % copies], x, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = geo.weight_bytes + M * K * 4 + M * N * 4
+    return {"ms": ms, "M": M, "N": N, "K": K, "algorithmic_bytes": int(nbytes),
+            "gbs": nbytes / (ms * 1e-3) / 1e9,
+            "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "path": lin_path(M), "launches_per_call": 2}
+
+
+def lin_path(m):
+    from sera_c_b200 import q4_linear
+    return q4_linear._L().q3_cuda_q4k_linear_path_for_batch(m).decode()
+
+
+CASES.update({
+    "q4k_qkv_fp32_1": lambda pkg, torch, dev, reps: case_q4k_mmvq(pkg, torch, dev, 1, reps=reps),
+    "q4k_qkv_fp32_8": lambda pkg, torch, dev, reps: case_q4k_mmvq(pkg, torch, dev, 8, reps=reps),
+})
+
+
 def run_extras(pkg, torch, device):
     """The other single-GPU configurations of the benchmark definition, one
     layer each: causal prefill (TFLOP/s), 8192-prefix cascade (tokens/s),

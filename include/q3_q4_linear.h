@@ -76,9 +76,13 @@ bool q3_cuda_q4k_linear_init(int device, size_t max_tokens, int64_t max_features
 size_t q3_cuda_q4k_linear_workspace_bytes(void);
 bool q3_cuda_q4k_linear_set_workspace(void *device_ptr, size_t bytes, char *error,
                                       size_t error_len);
-/* The reference answers "MMVQ" or "MMQ"; this library answers "MMA-small" (at
- * most 16 tokens, Q4_K in GGUF order: an mma.sync kernel without the tile pipeline)
- * or "TC" (the tcgen05 tile kernel). */
+/* Which arithmetic q3_cuda_q4k_linear applies to a batch. The reference answers
+ * "MMVQ" (at most 8 tokens) or "MMQ"; this library answers "MMVQ" for the same
+ * batches - the reference's own small-batch arithmetic: activations quantised
+ * to 8 bits per 32 elements, integer dot products, bound by the weight bytes -
+ * and "TC" above (f16 operands on the tensor cores). q3_cuda_q4k_linear_f16
+ * never quantises activations: at most 16 tokens take an mma.sync kernel,
+ * larger batches the tcgen05 tile kernel. */
 const char *q3_cuda_q4k_linear_path_for_batch(size_t token_count);
 
 /* Q4_K weight x fp32 activation -> fp32 output (ref: src/q3_q4_linear.h:93-108). */

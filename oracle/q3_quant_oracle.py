@@ -222,6 +222,52 @@ def candidate_logits_batched(hidden_per_branch, weight_bytes, qtype, candidate_i
     return np.einsum("ik,ik->i", w, h[b])
 
 
+# --------------------------------------------------------------------------
+# The reference's small-batch arithmetic: 8-bit activations, integer dots
+# --------------------------------------------------------------------------
+def q8_1_quantize(x):
+    """Per 32 elements: d = max|x| / 127 (fp32), q = round-half-away(x / d) as
+    int8 (0 when the block is all zero); the scale that enters the dot product
+    is d rounded to f16 (it is stored as a half next to the block sum). The
+    reference does this before its MMVQ / MMQ kernels (src/q3_q4_linear.h:6-14;
+    it vendors the ggml quantiser for it). Returns (q int32 [tokens, K],
+    d8 float64 [tokens, K/32])."""
+    x = np.asarray(x, np.float32)
+    t, k = x.shape
+    xb = x.reshape(t, k // 32, 32)
+    amax = np.abs(xb).max(axis=2)
+    d = (amax / np.float32(127.0)).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        r = (xb / d[:, :, None]).astype(np.float32)
+    q = np.where(amax[:, :, None] == 0, 0, np.sign(r) * np.floor(np.abs(r) + np.float32(0.5)))
+    return (q.reshape(t, k).astype(np.int32),
+            d.astype(np.float16).astype(np.float64))
+
+
+def q4k_linear_q8(weight_bytes, x):
+    """out[token][feature] = sum over blocks of
+         d * sum_i d8_i * sc_i * (q4 . q8)_i  -  dmin * sum_i d8_i * m_i * sum(q8)_i
+    over the eight 32-element sub-blocks i, in double: the arithmetic of the
+    reference's Q4_K x Q8_1 dot product, exact in the integers."""
+    n = weight_bytes.shape[0]
+    d, dmin, sc, mn, q4 = q4k_fields(weight_bytes)            # per block
+    nb = d.shape[0] // n                                      # blocks per row
+    q8, d8 = q8_1_quantize(x)
+    t = q8.shape[0]
+    q4 = q4.reshape(n, nb, 8, 32).astype(np.int64)
+    q8 = q8.reshape(t, nb, 8, 32).astype(np.int64)
+    d8 = d8.reshape(t, nb, 8)
+    dots = np.einsum("nbie,tbie->tnbi", q4, q8)               # exact integers
+    sums = q8.sum(axis=3)                                     # [t, nb, 8]
+    scd = sc.reshape(n, nb, 8).astype(np.float64)
+    mnd = mn.reshape(n, nb, 8).astype(np.float64)
+    dd = d.reshape(n, nb).astype(np.float64)
+    dm = dmin.reshape(n, nb).astype(np.float64)
+    part_d = np.einsum("tnbi,nbi,tbi->tnb", dots.astype(np.float64), scd, d8)
+    part_m = np.einsum("tbi,nbi,tbi->tnb", sums.astype(np.float64), mnd, d8)
+    return (part_d * dd[None] - part_m * dm[None]).sum(axis=2)
+
+
 def linear_error_metrics(got, ref):
     """The figures the reference's test prints and checks."""
     got = np.asarray(got, np.float64).reshape(-1)

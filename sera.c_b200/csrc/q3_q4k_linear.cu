@@ -49,6 +49,13 @@ bool q3_launch_q4k_small(const void *weight, const void *x_f16, uint32_t M, uint
                          uint32_t K, void *out, uint32_t out_type, cudaStream_t stream,
                          char *error, size_t error_len);
 
+/* q3_q4k_mmvq.cu */
+#define Q3_MMVQ_MAX_BATCH 8u
+size_t q3_q4k_mmvq_workspace_bytes(size_t tokens, size_t k);
+bool q3_launch_q4k_mmvq(const void *weight, const float *x, uint32_t M, uint32_t N, uint32_t K,
+                        float *out, void *workspace, cudaStream_t stream, char *error,
+                        size_t error_len);
+
 namespace {
 using namespace q3ptx;
 
@@ -708,7 +715,7 @@ extern "C" bool q3_cuda_q4k_linear_set_workspace(void *device_ptr, size_t bytes,
 }
 
 extern "C" const char *q3_cuda_q4k_linear_path_for_batch(size_t token_count) {
-    return token_count <= Q3_Q4K_SMALL_BATCH ? "MMA-small" : "TC";
+    return token_count <= Q3_MMVQ_MAX_BATCH ? "MMVQ" : "TC";
 }
 
 extern "C" bool q3_cuda_q4k_linear(const q3_q4_linear_geometry *geometry, const void *weight,
@@ -723,6 +730,9 @@ extern "C" bool q3_cuda_q4k_linear(const q3_q4_linear_geometry *geometry, const 
         return q3_fail(error, error_len, "q3_q4_linear: bad token count");
     if (geometry->N <= 0 || geometry->K <= 0)
         return q3_fail(error, error_len, "q3_q4_linear: unresolved geometry");
+    const bool mmvq = token_count <= Q3_MMVQ_MAX_BATCH && geometry->qtype == Q3_QUANT_Q4_K &&
+                      geometry->N % 128 == 0 && (((uintptr_t)weight | (uintptr_t)device_input |
+                                                  (uintptr_t)device_output) & 15u) == 0;
     const size_t need = token_count * (size_t)geometry->K * sizeof(__half);
     if (!g.workspace || need > g.workspace_attached)
         return q3_fail(error, error_len,
@@ -736,6 +746,18 @@ extern "C" bool q3_cuda_q4k_linear(const q3_q4_linear_geometry *geometry, const 
     }
     cudaStream_t st = (cudaStream_t)stream;
     cudaEventRecord(g.ev_begin, st);
+    if (mmvq) {
+        /* the reference's small-batch arithmetic: 8-bit activations, integer dots
+         * (its workspace need is below the f16 copy's, checked above) */
+        cudaEventRecord(g.ev_mid, st);
+        if (!q3_launch_q4k_mmvq(weight, device_input, (uint32_t)token_count,
+                                (uint32_t)geometry->N, (uint32_t)geometry->K, device_output,
+                                g.workspace, st, error, error_len))
+            return false;
+        cudaEventRecord(g.ev_end, st);
+        g.timed_convert = true;
+        return true;
+    }
     const size_t n8 = token_count * (size_t)geometry->K / 8;
     f32_to_f16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(
         device_input, static_cast<__half *>(g.workspace), n8);

@@ -115,8 +115,8 @@ def test_small_batch_path_matches_tile_kernel(lin):
     through the tiled order takes the tcgen05 kernel. Same operands, different
     summation order: equal to 1e-5 relative L2."""
     q4, L = lin
-    assert q4._L().q3_cuda_q4k_linear_path_for_batch(8) == b"MMA-small"
-    assert q4._L().q3_cuda_q4k_linear_path_for_batch(17) == b"TC"
+    assert q4._L().q3_cuda_q4k_linear_path_for_batch(8) == b"MMVQ"
+    assert q4._L().q3_cuda_q4k_linear_path_for_batch(9) == b"TC"
     w, x = _case(77, 13, 512, 2048)
     geo = q4.bind_geometry(2048, 512)
     wd = torch.from_numpy(w).cuda()
@@ -161,7 +161,14 @@ def test_fp32_surface_like_the_reference_test(lin, M):
     got = out.cpu().numpy()
     assert np.isfinite(got).all()
     m = qo.linear_error_metrics(got, qo.q4k_linear(w, x))
-    assert m["cos"] > 0.99999 and m["rel_l2"] < 1e-3, m
+    if M <= 8:
+        # the reference's small-batch arithmetic (8-bit activations): its own bar
+        # against the exact product, and 1e-5 against that arithmetic done exactly
+        assert m["cos"] > 0.999 and m["rel_l2"] < 0.01, m
+        mq = qo.linear_error_metrics(got, qo.q4k_linear_q8(w, x))
+        assert mq["rel_l2"] < 1e-5, mq
+    else:
+        assert m["cos"] > 0.99999 and m["rel_l2"] < 1e-3, m
     out2 = L.linear_f32(geo, wd, xd)
     torch.cuda.synchronize()
     assert torch.equal(out, out2)
@@ -208,7 +215,7 @@ def test_against_reference_kernels(lin):
                         dtype=torch.uint8, device="cuda")
     assert R.q3_cuda_q4k_linear_set_workspace(arena.data_ptr(), arena.numel(), err, 512), err.value
     N, K = 1024, 2048
-    for M in (1, 16, 64, 300):
+    for M in (1, 5, 8, 16, 64, 300):
         w, x = _case(100 + M, M, N, K)
         geo = q4.bind_geometry(K, N)
         wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
@@ -222,4 +229,10 @@ def test_against_reference_kernels(lin):
         mr = qo.linear_error_metrics(ref_out.cpu().numpy(), exact)
         mo = qo.linear_error_metrics(ours.cpu().numpy(), exact)
         assert mr["cos"] > 0.999 and mr["rel_l2"] < 0.03, (M, mr)
-        assert mo["rel_l2"] < 1e-3 and mo["rel_l2"] < mr["rel_l2"], (M, mo, mr)
+        if M <= 8:
+            # same arithmetic as the reference's MMVQ path: the two results agree
+            # to fp32 summation order (and the odd x/d tie under its fast-math build)
+            both = qo.linear_error_metrics(ours.cpu().numpy(), ref_out.cpu().numpy())
+            assert both["rel_l2"] < 1e-4, (M, both)
+        else:
+            assert mo["rel_l2"] < 1e-3 and mo["rel_l2"] < mr["rel_l2"], (M, mo, mr)

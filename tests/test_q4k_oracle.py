@@ -120,3 +120,17 @@ def test_q6k_f16_operand_model_is_close_to_exact():
     exact = qo.q6k_dequantize(blocks).astype(np.float64)
     f16 = qo.q6k_dequantize_f16_operands(blocks).astype(np.float64)
     assert np.abs(f16 - exact).max() <= 2e-3 * np.abs(exact).max()
+
+
+def test_q8_activation_model():
+    """Q8_1 quantisation and the integer dot: error against the exact product is
+    at the level the reference accepts (1 %); an all-zero block quantises to zero."""
+    rng = np.random.default_rng(8)
+    w = qo.q4k_weight(rng, 16, 1024)
+    x = rng.standard_normal((3, 1024)).astype(np.float32)
+    x[1, 64:96] = 0.0
+    q, d8 = qo.q8_1_quantize(x)
+    assert np.abs(q).max() == 127 and not q[1, 64:96].any() and d8[1, 2] == 0.0
+    assert np.abs(q * np.repeat(d8, 32, axis=1) - x).max() <= 0.51 * d8.max() * 1.001
+    m = qo.linear_error_metrics(qo.q4k_linear_q8(w, x), qo.q4k_linear(w, x))
+    assert m["rel_l2"] < 0.02 and m["cos"] > 0.999
