@@ -67,3 +67,34 @@ def test_bad_candidate_and_arguments(head):
         head.candidate_logits_batched(h, w, 2, 10, ids, 2)
     with pytest.raises(Q3Error, match="invalid argument"):
         head.candidate_logits_batched(torch.zeros(1, 100, device="cuda"), w, 12, 10, ids, 2)
+
+
+@pytest.mark.parametrize("name", ["config1", "ragged"])
+def test_argmax_identical_through_the_candidate_head(head, name):
+    """The path's own consumer: the attention rows of the packed suffix (GPU,
+    fp32 output) go through q3_cuda_candidate_head with a Q6_K weight whose
+    row length is the attention width; the per-branch decision must equal the
+    one the oracle reaches from the oracle's attention rows."""
+    import _cases
+    import _gpu_harness as harness
+    import q3_oracle as oracle
+    pkg = entry.load_package()
+    case = harness.rounded_case(_cases.make_case(name))
+    ref = oracle.run_case(case)["out"]                     # [T, H, D]
+    got = harness.run_case_native(pkg, case, out_fp32=True)
+    P, S, width, K = case.P, case.S, case.H * case.D, 5
+    vocab = 64
+    rng = np.random.default_rng(17)
+    w = qo.q6k_random_blocks(rng, vocab * (width // 256)).reshape(vocab, -1)
+    B = len(case.branch_lens)
+    ids = rng.integers(0, vocab, B * K).astype(np.int32)
+    offs = case.branch_offsets.astype(np.int32)            # offsets inside the suffix
+    rows = torch.from_numpy(np.ascontiguousarray(got[P:].reshape(S, width))).cuda()
+    logits, best = head.candidate_head(rows, torch.from_numpy(offs).cuda(),
+                                       torch.from_numpy(w).cuda(), 14, vocab,
+                                       torch.from_numpy(ids).cuda(), K)
+    torch.cuda.synchronize()
+    want = qo.candidate_logits_batched(
+        qo.gather_last_rows(ref[P:].reshape(S, width), offs), w, 14, ids, K).reshape(B, K)
+    assert np.array_equal(best.cpu().numpy(), want.argmax(axis=1))
+    assert np.abs(logits.cpu().numpy().reshape(B, K) - want).max() < 2e-3 * np.abs(want).max()
