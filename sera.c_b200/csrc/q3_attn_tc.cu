@@ -592,7 +592,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                         float x0, x1, p0, p1;
                         const uint64_t x2 = ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, neg2);
                         unpack2(x2, x0, x1);
-                        if ((i & 7u) < Q3_POLY_PAIRS_OF_8) {
+                        if ((int)(i & 7u) < (int)Q3_POLY_PAIRS_OF_8) {
                             exp2_poly2(pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f)), p0, p1);
                         } else {
                             p0 = fast_exp2(x0);
