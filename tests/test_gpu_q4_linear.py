@@ -110,6 +110,35 @@ def test_q6k_weight_through_the_tiled_layout(lin, M, N, K):
     assert exact["rel_l2"] < 1e-3 and exact["cos"] > 0.99999, exact
 
 
+@pytest.mark.parametrize("qtype", [12, 14])
+@pytest.mark.parametrize("M,N,K", [(600, 8192, 256), (600, 8192, 1024), (1500, 10240, 512)])
+def test_more_tiles_than_sms(lin, qtype, M, N, K):
+    """The tile kernel is persistent: with more output tiles than SMs a CTA walks
+    several tiles, its rings run on across the tile boundary and the accumulator
+    is drained while the next tile's operands are converted. K = 256 is the
+    shortest row (4 k-steps per tile: a group crosses a tile boundary after one or
+    two steps). Every output is checked."""
+    q4, L = lin
+    plan = q4.plan(M, N)
+    assert plan.tiles > 148 and plan.tiles_per_cta_max >= 2
+    rng = np.random.default_rng(M + N + K + qtype)
+    nb = N * (K // 256)
+    w = (qo.q4k_random_blocks(rng, nb) if qtype == 12 else qo.q6k_random_blocks(rng, nb))
+    w = w.reshape(N, -1)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    geo = q4.bind_geometry(K, N, qtype=qtype)
+    wd = torch.from_numpy(w).cuda()
+    xd = torch.from_numpy(x).cuda().half()
+    if qtype == 14:
+        wd, geo = L.pack(geo, wd)
+    got = L.linear_f16(geo, wd, xd, out_dtype=torch.float32).cpu().numpy()
+    assert L.status() == 0
+    ref16 = qo.quant_linear(w, qtype, x, operands="f16")
+    err = np.abs(got - ref16)
+    assert err.max() < 1e-3 * np.abs(ref16).max(), np.unravel_index(err.argmax(), err.shape)
+    assert qo.linear_error_metrics(got, ref16)["rel_l2"] < 1e-4
+
+
 def test_small_batch_path_matches_tile_kernel(lin):
     """At most 16 tokens take the mma.sync kernel (GGUF order); the same batch
     through the tiled order takes the tcgen05 kernel. Same operands, different
