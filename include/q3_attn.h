@@ -146,6 +146,11 @@ bool q3_attn_set_qk_norm(q3_attn_runtime *rt, uint32_t layer,
 void *q3_attn_stream(const q3_attn_runtime *rt);
 /* ref: src/q3_forward.h:163-164 - the explicit measurement-boundary sync. */
 bool q3_attn_synchronize(q3_attn_runtime *rt, char *error, size_t error_len);
+/* After q3_attn_synchronize reported that a kernel gave up a bounded wait:
+ * queues, on the runtime's stream, the clearing of the status word and of the
+ * arrival counters that launch may have left part-way. Required before the
+ * runtime is used again; results of the launch that timed out are undefined. */
+bool q3_attn_reset_status(q3_attn_runtime *rt, char *error, size_t error_len);
 
 typedef struct {
     uint64_t cuda_allocations;   /* since create; constant in the warm path   */
@@ -167,7 +172,8 @@ void q3_attn_get_stats(const q3_attn_runtime *rt, q3_attn_stats *stats);
  * pairs, created here, none in the warm path). q3_attn_phase_times
  * synchronises the stream, SUMS the pairs recorded since the last call per
  * phase, and rewinds. Phases: 0 fused norm+rope+KV write, 1 tensor-core
- * attention, 2 partial merge, 3 paged decode (+ its merge). */
+ * attention, 2 waits for the other ranks' rows (q3_attn_wait_gathered: the
+ * part of the output exchange that is not hidden), 3 paged decode (+ its merge). */
 bool q3_attn_enable_timing(q3_attn_runtime *rt, uint32_t max_launches, char *error,
                            size_t error_len);
 bool q3_attn_phase_times(q3_attn_runtime *rt, double ms_out[4],
@@ -405,9 +411,14 @@ bool q3_decode_attention_layer(q3_decode_plan *plan, uint32_t layer,
  *   out_bf16     [num_seqs][n_heads][128] bf16
  * Limit: n_work * n_kv_heads <= Q3_DECODE_NOALLOC_MAX_SLOTS, else the call
  * fails with a message. The first call on each device looks up the array's
- * device address; make that call before any stream capture. All calls share the
- * array: two calls that overlap on the GPU race. Nothing in it needs clearing
- * (every slot a call reads was written by that call). */
+ * device address (safe from several host threads); make that call before any
+ * stream capture. All calls share the array: two calls that overlap on the GPU
+ * race. Nothing in it needs clearing (every slot a call reads was written by
+ * that call). The pools are the caller's: slots past ctx_len in a sequence's
+ * last page are multiplied by an exact 0 and must therefore hold finite values
+ * (a zero-initialised pool does). Every ctx_len must be >= 1. The kernel's waits
+ * are bounded; q3_cuda_attention_decode_noalloc_status tells whether one gave
+ * up (the rows of that call are then undefined). */
 #define Q3_DECODE_NOALLOC_MAX_SLOTS 2048u
 typedef struct {
     uint32_t seq;
@@ -427,6 +438,12 @@ bool q3_cuda_attention_decode_noalloc(
     const q3_decode_work_item *work, uint32_t n_work, const uint32_t *seq_work_begin,
     uint32_t num_seqs, uint32_t n_heads, uint32_t n_kv_heads, void *out_bf16,
     void *stream, char *error, size_t error_len);
+/* Copies the current device's status word of the entry above into *status_out
+ * (host memory), clears it and synchronises `stream`: 0 = every wait of the
+ * calls queued so far on that stream completed; nonzero = one gave up. Also
+ * allocates nothing. No counterpart in the reference. */
+bool q3_cuda_attention_decode_noalloc_status(uint32_t *status_out, void *stream,
+                                             char *error, size_t error_len);
 
 /* --- low-level fused KV write (new kernel; replaces ref a1+a2/a3+a5/a8:
  *     two rms_norm launches, rope, and the append / scatter) -------------- *
@@ -474,7 +491,7 @@ typedef struct {
 typedef struct {
     uint32_t grid;
     uint32_t n_segments;
-    uint32_t n_merges;
+    uint32_t n_cut_items;
     uint32_t n_slots;
     uint64_t total_key_tiles;
 } q3_sched_summary;
@@ -484,6 +501,17 @@ bool q3_schedule_describe(uint32_t tokens, uint32_t n_kv_heads, uint32_t shared_
                           uint32_t num_ctas, uint32_t max_slots, bool lockstep,
                           q3_sched_summary *summary, q3_sched_segment_info *segments,
                           uint32_t max_segments, char *error, size_t error_len);
+
+/* Which of the two assignments of key tiles to CTAs a packed batch gets
+ * (plans built after the call). AUTO: lockstep waves when the shared KV of the
+ * runtime's heads is larger than L2 holds comfortably, stream-K otherwise.
+ * Both give the same rows up to the rounding of the partial combination; the
+ * knob exists for tuning and so that tests can run either on any shape. */
+#define Q3_SCHED_AUTO 0u
+#define Q3_SCHED_STREAMK 1u
+#define Q3_SCHED_LOCKSTEP 2u
+bool q3_attn_set_schedule_policy(q3_attn_runtime *rt, uint32_t policy, char *error,
+                                 size_t error_len);
 
 const char *q3_attn_version(void);
 

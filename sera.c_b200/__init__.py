@@ -75,7 +75,7 @@ class SchedSegmentInfo(ctypes.Structure):
 
 class SchedSummary(ctypes.Structure):
     _fields_ = [("grid", ctypes.c_uint32), ("n_segments", ctypes.c_uint32),
-                ("n_merges", ctypes.c_uint32), ("n_slots", ctypes.c_uint32),
+                ("n_cut_items", ctypes.c_uint32), ("n_slots", ctypes.c_uint32),
                 ("total_key_tiles", ctypes.c_uint64)]
 
 
@@ -139,12 +139,15 @@ class Runtime:
     def synchronize(self):
         _call(lib().q3_attn_synchronize, self.h)
 
+    def reset_status(self):
+        _call(lib().q3_attn_reset_status, self.h)
+
     def stats(self):
         s = AttnStats()
         lib().q3_attn_get_stats(self.h, ctypes.byref(s))
         return s
 
-    PHASES = ("kvwrite", "attention", "merge", "decode")
+    PHASES = ("kvwrite", "attention", "gather_wait", "decode")
 
     def enable_timing(self, max_launches=4096):
         _call(lib().q3_attn_enable_timing, self.h, max_launches)
@@ -155,6 +158,11 @@ class Runtime:
         n = (ctypes.c_uint64 * 4)()
         _call(lib().q3_attn_phase_times, self.h, ms, n)
         return {name: (ms[i], int(n[i])) for i, name in enumerate(self.PHASES)}
+
+    SCHED = {"auto": 0, "streamk": 1, "lockstep": 2}
+
+    def set_schedule_policy(self, policy):
+        _call(lib().q3_attn_set_schedule_policy, self.h, self.SCHED[policy])
 
     def gather_advance(self, count):
         _call(lib().q3_attn_gather_advance, self.h, count)
@@ -412,6 +420,15 @@ def attention_decode_noalloc(q_f16, k_pages, v_pages, ctx_lens, page_indptr, pag
           num_pages, _ptr(ctx_lens), _ptr(page_indptr), _ptr(page_indices), _ptr(work),
           work.shape[0], _ptr(seq_work_begin), q_f16.shape[0], q_f16.shape[1], n_kv_heads,
           _ptr(out_bf16), ctypes.c_void_p(stream_ptr) if stream_ptr else None)
+
+
+def attention_decode_noalloc_status(stream_ptr=None):
+    """q3_cuda_attention_decode_noalloc_status: reads and clears the status word
+    of the allocation-free decode entry on the current device (synchronises)."""
+    st = ctypes.c_uint32(0xFFFFFFFF)
+    _call(lib().q3_cuda_attention_decode_noalloc_status, ctypes.byref(st),
+          ctypes.c_void_p(stream_ptr) if stream_ptr else None)
+    return int(st.value)
 
 
 def pack_suffix_host(items, prefix_len, max_branches, max_suffix):

@@ -191,9 +191,12 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     sig("q3_decode_work_host", ctypes.c_int64, [up, u32, vp, u32, up] + err)
     sig("q3_cuda_attention_decode_noalloc", b,
         [vp, vp, vp, u32, vp, vp, vp, vp, u32, vp, u32, u32, u32, vp, vp] + err)
+    sig("q3_cuda_attention_decode_noalloc_status", b, [up, vp] + err)
+    sig("q3_attn_reset_status", b, [vp] + err)
     sig("q3_cuda_qknorm_rope_kvwrite", b, [vp, u32, vp, vp, vp, u32, vp, vp, vp, vp] + err)
     sig("q3_schedule_describe", b,
         [u32, u32, u32, up, up, u32, u32, u32, u32, b, ctypes.POINTER(SchedSummary),
          ctypes.POINTER(SchedSegmentInfo), u32] + err)
+    sig("q3_attn_set_schedule_policy", b, [vp, u32] + err)
     sig("q3_attn_version", ctypes.c_char_p, [])
     return L

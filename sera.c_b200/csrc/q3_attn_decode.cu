@@ -22,6 +22,8 @@
 #include "q3_internal.h"
 #include "q3_ptx.cuh"
 
+#include <mutex>
+
 using namespace q3ptx;
 
 namespace {
@@ -96,7 +98,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
     const q3_decode_work w = p.work[blockIdx.x];
     const uint32_t h = blockIdx.y;
     const uint32_t n_keys = p.ctx_lens[w.seq] + p.extra_token;
-    const uint32_t n_pages = w.page_end - w.page_begin;
+    /* The work list may have been cut for one more key than this call sees
+     * (a plan serves calls with and without an appended token): never touch a
+     * page that holds no visible key, it may lie past the sequence's list. */
+    const uint32_t page_end = min(w.page_end, (n_keys + Q3_PAGE - 1) / Q3_PAGE);
+    const uint32_t n_pages = page_end > w.page_begin ? page_end - w.page_begin : 0u;
     const uint32_t n_tiles = (n_pages + kDecTilePages - 1) / kDecTilePages;
 
     if (threadIdx.x == 0) {
@@ -271,7 +277,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
         }
         const bool single = p.seq_work_begin[w.seq + 1] - p.seq_work_begin[w.seq] == 1;
         if (single && p.out_fp32) {
-            const float inv = 1.0f / den;
+            const float inv = den > 0.f ? 1.0f / den : 0.f;   /* no visible key: zeros */
             float *dst = reinterpret_cast<float *>(p.out) +
                          ((size_t)w.seq * p.n_heads + h * Q3_G + r) * Q3_D + d0;
             *reinterpret_cast<float4 *>(dst) =
@@ -279,7 +285,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
             *reinterpret_cast<float4 *>(dst + 4) =
                 make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
         } else if (single) {
-            const float inv = 1.0f / den;
+            const float inv = den > 0.f ? 1.0f / den : 0.f;
             uint4 u;
             __nv_bfloat162 *hh = reinterpret_cast<__nv_bfloat162 *>(&u);
 #pragma unroll
@@ -289,7 +295,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap k_map,
                 reinterpret_cast<__nv_bfloat16 *>(p.out) +
                 ((size_t)w.seq * p.n_heads + h * Q3_G + r) * Q3_D + d0) = u;
         } else {
-            const size_t slot = (size_t)w.slot * p.n_kv_heads + h;
+            /* the partial slot is the work item's index (the merge kernel walks
+             * seq_work_begin the same way); a caller-written `slot` field is
+             * not trusted with an index into the fixed scratch */
+            const size_t slot = (size_t)blockIdx.x * p.n_kv_heads + h;
             float *dst = p.part_o + (slot * 8 + r) * Q3_D + d0;
             *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
             *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
@@ -328,7 +337,7 @@ decode_merge_kernel(const uint32_t *__restrict__ seq_work_begin, uint32_t num_se
         acc.z += wgt * o.z;
         acc.w += wgt * o.w;
     }
-    const float inv = 1.0f / den;
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
     const size_t off = ((size_t)seq * n_heads + head) * Q3_D + lane * 4;
     if (out_fp32) {
         *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + off) =
@@ -423,6 +432,39 @@ struct NoallocDevice {
     uint32_t *status;
 };
 NoallocDevice g_noalloc[64];
+std::mutex g_noalloc_mutex;   /* first-call set-up may race between host threads */
+
+/* Looks up the scratch addresses of the current device once. */
+bool noalloc_device(NoallocDevice **out, const char *who, char *error, size_t error_len) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        if (error && error_len) snprintf(error, error_len, "%s: no current device", who);
+        return false;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoallocDevice &nd = g_noalloc[dev];
+    if (!nd.ready) {
+        /* The array names are host-side stand-ins, not device addresses; ask the
+         * runtime for the addresses once, with this device current. */
+        cudaError_t e = cudaGetSymbolAddress((void **)&nd.part_o, q3_noalloc_part_o);
+        if (e == cudaSuccess)
+            e = cudaGetSymbolAddress((void **)&nd.part_ml, q3_noalloc_part_ml);
+        if (e == cudaSuccess)
+            e = cudaGetSymbolAddress((void **)&nd.status, q3_noalloc_status);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(decode_attention_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kDecSmemTotal);
+        if (e != cudaSuccess) {
+            if (error && error_len)
+                snprintf(error, error_len, "%s: device set-up: %s", who, cudaGetErrorString(e));
+            return false;
+        }
+        nd.ready = true;
+    }
+    *out = &nd;
+    return true;
+}
 }  // namespace
 
 static_assert(sizeof(q3_decode_work_item) == sizeof(q3_decode_work),
@@ -437,6 +479,11 @@ extern "C" int64_t q3_decode_work_host(const uint32_t *ctx_lens, uint32_t num_se
         q3_fail(error, error_len, "q3_decode_work_host: invalid argument");
         return -1;
     }
+    for (uint32_t s = 0; s < num_seqs; s++)
+        if (ctx_lens[s] == 0) {
+            q3_fail(error, error_len, "q3_decode_work_host: a sequence has no context");
+            return -1;
+        }
     std::vector<q3_decode_work> work;
     std::vector<uint32_t> swb;
     q3_build_decode_work(ctx_lens, num_seqs, 0, 64, work, swb);
@@ -471,28 +518,9 @@ extern "C" bool q3_cuda_attention_decode_noalloc(
     const uint64_t rows = (uint64_t)n_kv_heads * num_pages * Q3_PAGE;
     if (rows >= (1ull << 31))
         return q3_fail(error, error_len, "q3_cuda_attention_decode_noalloc: pool too large");
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
-        return q3_fail(error, error_len, "q3_cuda_attention_decode_noalloc: no current device");
-    NoallocDevice &nd = g_noalloc[dev];
-    if (!nd.ready) {
-        /* First call on this device: the array names above are host-side
-         * stand-ins, not device addresses; ask the runtime for the addresses
-         * once, with this device current. */
-        cudaError_t e = cudaGetSymbolAddress((void **)&nd.part_o, q3_noalloc_part_o);
-        if (e == cudaSuccess)
-            e = cudaGetSymbolAddress((void **)&nd.part_ml, q3_noalloc_part_ml);
-        if (e == cudaSuccess)
-            e = cudaGetSymbolAddress((void **)&nd.status, q3_noalloc_status);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(decode_attention_kernel,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)kDecSmemTotal);
-        if (e != cudaSuccess)
-            return q3_fail_cuda(error, error_len,
-                                "q3_cuda_attention_decode_noalloc: device set-up", e);
-        nd.ready = true;
-    }
+    NoallocDevice *ndp = nullptr;
+    if (!noalloc_device(&ndp, "q3_cuda_attention_decode_noalloc", error, error_len)) return false;
+    NoallocDevice &nd = *ndp;
     CUtensorMap k_map, v_map;   /* host-side encoding, no device memory involved */
     if (!q3_encode_tmap_2d(&k_map, k_pages, Q3_D, rows, 64, Q3_PAGE, error, error_len) ||
         !q3_encode_tmap_2d(&v_map, v_pages, Q3_D, rows, 64, Q3_PAGE, error, error_len))
@@ -527,5 +555,24 @@ extern "C" bool q3_cuda_attention_decode_noalloc(
             out_bf16);
         Q3_LAUNCH_CHECK("q3_cuda_attention_decode_noalloc: merge launch failed");
     }
+    return true;
+}
+
+extern "C" bool q3_cuda_attention_decode_noalloc_status(uint32_t *status_out, void *stream,
+                                                        char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!status_out)
+        return q3_fail(error, error_len,
+                       "q3_cuda_attention_decode_noalloc_status: invalid argument");
+    NoallocDevice *nd = nullptr;
+    if (!noalloc_device(&nd, "q3_cuda_attention_decode_noalloc_status", error, error_len))
+        return false;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(status_out, nd->status, sizeof(uint32_t),
+                                    cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(nd->status, 0, sizeof(uint32_t), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess)
+        return q3_fail_cuda(error, error_len, "q3_cuda_attention_decode_noalloc_status", e);
     return true;
 }

@@ -793,8 +793,10 @@ bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint
 
 bool q3_launch_gather_wait(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
                            char *error, size_t error_len) {
+    q3_phase_begin(rt, Q3_PHASE_GATHER_WAIT);
     gather_wait_kernel<<<1, 32, 0, rt->stream>>>(g->flags[g->rank], g->n_ranks, seq,
                                                  rt->gather_epoch_dev, rt->status_dev);
+    q3_phase_end(rt);
     Q3_LAUNCH_CHECK("gather_wait launch failed");
     rt->n_launch++;
     return true;

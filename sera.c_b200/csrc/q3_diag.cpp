@@ -1,7 +1,7 @@
 /* q3_diag.cpp - pure-host inspection of the launch schedule through the C ABI
  * (no CUDA call): lets tests check on a machine without a GPU that every key
- * tile of every item is covered exactly once and that cut items have merge
- * entries. */
+ * tile of every item is covered exactly once and that the pieces of cut items
+ * have partial slots of their own. */
 #include <string.h>
 
 #include "q3_attn.h"
@@ -32,7 +32,7 @@ extern "C" bool q3_schedule_describe(uint32_t tokens, uint32_t n_kv_heads,
         return false;
     summary->grid = s.grid;
     summary->n_segments = (uint32_t)s.segments.size();
-    summary->n_merges = (uint32_t)s.merges.size();
+    summary->n_cut_items = s.n_cut_items;
     summary->n_slots = s.n_slots;
     summary->total_key_tiles = s.total_key_tiles;
     if (segments) {

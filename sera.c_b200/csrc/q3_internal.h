@@ -107,6 +107,7 @@ struct q3_attn_runtime {
 
     uint64_t n_alloc, n_free, n_sync, n_launch;
     uint64_t workspace_bytes;
+    uint32_t sched_policy;       /* Q3_SCHED_AUTO / _STREAMK / _LOCKSTEP */
 
     /* optional per-kernel timing: event pairs recorded around launches, read
      * after a synchronize (the reference brackets its phases the same way,
@@ -117,7 +118,7 @@ struct q3_attn_runtime {
     size_t ev_used;                   /* pairs recorded */
 };
 
-enum { Q3_PHASE_KVWRITE = 0, Q3_PHASE_ATTENTION = 1, Q3_PHASE_MERGE = 2,
+enum { Q3_PHASE_KVWRITE = 0, Q3_PHASE_ATTENTION = 1, Q3_PHASE_GATHER_WAIT = 2,
        Q3_PHASE_DECODE = 3, Q3_PHASE_COUNT = 4 };
 
 static inline void q3_phase_begin(q3_attn_runtime *rt, int phase) {
@@ -171,12 +172,10 @@ struct q3_stage {
     const uint32_t *rope_pos, *dst_page, *dst_slot;
     const uint32_t *row_tag, *row_lp;
     const uint32_t *page_ids;
-    const uint32_t *tile_run_begin;
     const q3_run *runs;
     const q3_segment *segments;
     const uint32_t *cta_seg_begin;
-    const q3_merge_item *merges;
-    uint32_t tokens, n_shared_pages, shared_len, grid, n_merges;
+    uint32_t tokens, n_shared_pages, shared_len, grid;
     /* prefill chunks: which (base, tokens) the staged schedule describes */
     bool chunk_valid;
     uint32_t chunk_base, chunk_tokens;
@@ -197,6 +196,7 @@ struct q3_decode_plan {
     uint32_t n_work;     /* (sequence, chunk) work items per KV head */
     uint32_t chunk_pages;
     bool can_append;     /* every sequence has a page slot for one more token */
+    bool has_empty;      /* some sequence has ctx_len 0 (needs an appended token) */
     void *dev;
     const uint32_t *ctx_lens, *page_indptr, *page_indices;
     const uint32_t *rope_pos, *dst_page, *dst_slot;

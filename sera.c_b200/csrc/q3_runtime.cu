@@ -200,6 +200,7 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     rt->capture_launches = 0;
     rt->n_alloc = rt->n_free = rt->n_sync = rt->n_launch = 0;
     rt->workspace_bytes = 0;
+    rt->sched_policy = Q3_SCHED_AUTO;
     rt->timing_on = false;
     rt->ev_used = 0;
 
@@ -348,6 +349,15 @@ extern "C" bool q3_attn_set_qk_norm(q3_attn_runtime *rt, uint32_t layer,
     return true;
 }
 
+extern "C" bool q3_attn_set_schedule_policy(q3_attn_runtime *rt, uint32_t policy,
+                                            char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt || policy > Q3_SCHED_LOCKSTEP)
+        return q3_fail(error, error_len, "q3_attn_set_schedule_policy: invalid argument");
+    rt->sched_policy = policy;
+    return true;
+}
+
 extern "C" void *q3_attn_stream(const q3_attn_runtime *rt) {
     return rt ? (void *)rt->stream : NULL;
 }
@@ -371,6 +381,20 @@ extern "C" bool q3_attn_synchronize(q3_attn_runtime *rt, char *error,
                      *rt->status_host);
         return false;
     }
+    return true;
+}
+
+extern "C" bool q3_attn_reset_status(q3_attn_runtime *rt, char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!rt) return q3_fail(error, error_len, "q3_attn_reset_status: null runtime");
+    if (!q3_use_device(rt, error, error_len)) return false;
+    /* A launch that gave up a wait may have left arrival counters of cut items
+     * part-way: clear them together with the status word, in stream order. */
+    cudaError_t e = cudaMemsetAsync(rt->fix_counters, 0,
+                                    (size_t)rt->part_slots * 8 * sizeof(uint32_t), rt->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(rt->status_dev, 0, sizeof(uint32_t), rt->stream);
+    if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "q3_attn_reset_status", e);
+    *rt->status_host = 0;
     return true;
 }
 
@@ -506,11 +530,9 @@ bool q3_stage_upload(q3_stage *st, const q3_schedule &s,
     need = put<uint32_t>(nullptr, need, s.row_tag, nullptr, nullptr);
     need = put<uint32_t>(nullptr, need, s.row_lp, nullptr, nullptr);
     need = put<uint32_t>(nullptr, need, s.page_ids, nullptr, nullptr);
-    need = put<uint32_t>(nullptr, need, s.tile_run_begin, nullptr, nullptr);
     need = put<q3_run>(nullptr, need, s.runs, nullptr, nullptr);
     need = put<q3_segment>(nullptr, need, s.segments, nullptr, nullptr);
     need = put<uint32_t>(nullptr, need, s.cta_seg_begin, nullptr, nullptr);
-    need = put<q3_merge_item>(nullptr, need, s.merges, nullptr, nullptr);
     need += 64;
     if (need > st->bytes) {
         cudaStreamSynchronize(rt->stream); /* growth is set-up, not warm path */
@@ -537,16 +559,13 @@ bool q3_stage_upload(q3_stage *st, const q3_schedule &s,
     off = put<uint32_t>(h, off, s.row_tag, &st->row_tag, d);
     off = put<uint32_t>(h, off, s.row_lp, &st->row_lp, d);
     off = put<uint32_t>(h, off, s.page_ids, &st->page_ids, d);
-    off = put<uint32_t>(h, off, s.tile_run_begin, &st->tile_run_begin, d);
     off = put<q3_run>(h, off, s.runs, &st->runs, d);
     off = put<q3_segment>(h, off, s.segments, &st->segments, d);
     off = put<uint32_t>(h, off, s.cta_seg_begin, &st->cta_seg_begin, d);
-    off = put<q3_merge_item>(h, off, s.merges, &st->merges, d);
     st->tokens = s.tokens;
     st->n_shared_pages = s.n_shared_pages;
     st->shared_len = s.shared_len;
     st->grid = s.grid;
-    st->n_merges = (uint32_t)s.merges.size();
     cudaError_t e = cudaMemcpyAsync(st->dev, st->host, off, cudaMemcpyHostToDevice,
                                     rt->stream);
     if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "stage: upload", e);
@@ -887,6 +906,8 @@ extern "C" int64_t q3_pack_suffix_host(const q3_suffix_item *items, uint32_t cou
 /* Staggered stream-K access keeps the shared KV of ALL local heads live at
  * once; when that exceeds what L2 holds comfortably, walk items in lockstep. */
 static bool q3_prefers_lockstep(const q3_attn_runtime *rt, uint32_t shared_len) {
+    if (rt->sched_policy == Q3_SCHED_STREAMK) return false;
+    if (rt->sched_policy == Q3_SCHED_LOCKSTEP) return true;
     const uint64_t kv_bytes = (uint64_t)((shared_len + Q3_PAGE - 1) / Q3_PAGE) * 2 * 4096 *
                               rt->cfg.n_kv_heads;
     return kv_bytes > (48ull << 20);
@@ -1317,6 +1338,9 @@ extern "C" q3_decode_plan *q3_decode_plan_create(q3_attn_runtime *rt,
     plan->rt = rt;
     plan->num_seqs = num_seqs;
     plan->can_append = can_append;
+    plan->has_empty = false;
+    for (uint32_t s = 0; s < num_seqs; s++)
+        if (ctx_lens[s] == 0) plan->has_empty = true;
     /* Chunks of 64 pages (1024 keys, 256 KiB of K+V per head): long enough to
      * amortise the pipeline fill, short enough to balance ragged contexts. */
     plan->chunk_pages = 64;
@@ -1399,6 +1423,9 @@ extern "C" bool q3_decode_attention_layer(q3_decode_plan *plan, uint32_t layer,
     if (!q3_use_device(rt, error, error_len)) return false;
     if (layer >= rt->cfg.num_layers)
         return q3_fail(error, error_len, "q3_decode_attention_layer: layer out of range");
+    if (!k_new && plan->has_empty)
+        return q3_fail(error, error_len,
+                       "q3_decode_attention_layer: a sequence has no context and no new token");
     if (k_new && !plan->can_append)
         return q3_fail(error, error_len,
                        "q3_decode_attention_layer: a sequence has no page for the new token");

@@ -41,10 +41,10 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
     /* Runs: distinct branches of each token tile, in order of first
      * appearance, each with the pages its rows can see. */
     const uint32_t n_tok_tiles = (tokens + Q3_TOK_TILE - 1) / Q3_TOK_TILE;
-    s.tile_run_begin.resize(n_tok_tiles + 1);
+    std::vector<uint32_t> tile_run_begin(n_tok_tiles + 1);
     std::vector<uint32_t> tile_private_pages(n_tok_tiles);
     for (uint32_t tt = 0; tt < n_tok_tiles; tt++) {
-        s.tile_run_begin[tt] = (uint32_t)s.runs.size();
+        tile_run_begin[tt] = (uint32_t)s.runs.size();
         const uint32_t t0 = tt * Q3_TOK_TILE;
         const uint32_t t1 = std::min(tokens, t0 + Q3_TOK_TILE);
         const size_t first = s.runs.size();
@@ -76,7 +76,7 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
         for (size_t r = first; r < s.runs.size(); r++) pages += s.runs[r].n_pages;
         tile_private_pages[tt] = pages;
     }
-    s.tile_run_begin[n_tok_tiles] = (uint32_t)s.runs.size();
+    tile_run_begin[n_tok_tiles] = (uint32_t)s.runs.size();
 
     /* Items in (kv_head, token tile) order and their key-tile counts. */
     const uint32_t shared_tiles =
@@ -153,7 +153,7 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
             }
         }
     }
-    /* Flatten; cut items get consecutive partial slots and a merge entry. */
+    /* Flatten; cut items get consecutive partial slots. */
     std::vector<uint32_t> item_pieces(items.size(), 0), item_slot(items.size(), 0);
     for (uint32_t c = 0; c < grid; c++)
         for (const Piece &pc : per_cta[c]) item_pieces[pc.item]++;
@@ -161,14 +161,9 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
         if (item_pieces[i] > 1) {
             if (s.n_slots + item_pieces[i] > max_slots)
                 return sched_fail(error, error_len, "schedule: out of partial slots");
-            q3_merge_item m;
-            m.tok0 = items[i].tt * Q3_TOK_TILE;
-            m.kv_head = items[i].h;
-            m.slot_begin = s.n_slots;
-            m.slot_count = item_pieces[i];
             item_slot[i] = s.n_slots;
             s.n_slots += item_pieces[i];
-            s.merges.push_back(m);
+            s.n_cut_items++;
         }
     }
     std::vector<uint32_t> item_next(items.size(), 0), item_fix(items.size(), 0);
@@ -194,8 +189,8 @@ bool q3_build_schedule(q3_schedule &s, uint32_t tokens, uint32_t n_kv_heads,
             seg.partial_slot = item_pieces[pc.item] > 1
                                    ? (int32_t)(item_slot[pc.item] + item_next[pc.item]++)
                                    : -1;
-            seg.run_begin = s.tile_run_begin[it.tt];
-            seg.run_end = s.tile_run_begin[it.tt + 1];
+            seg.run_begin = tile_run_begin[it.tt];
+            seg.run_end = tile_run_begin[it.tt + 1];
             seg.slot_begin = item_slot[pc.item];
             seg.slot_count = item_pieces[pc.item] > 1 ? item_pieces[pc.item] : 0;
             seg.fix_index = item_fix[pc.item];

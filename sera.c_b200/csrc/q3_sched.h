@@ -50,13 +50,6 @@ struct q3_segment {
     uint32_t pad;
 };
 
-struct q3_merge_item {
-    uint32_t tok0;
-    uint32_t kv_head;
-    uint32_t slot_begin;
-    uint32_t slot_count;
-};
-
 struct q3_decode_work {
     uint32_t seq;
     uint32_t page_begin;   /* pages [page_begin, page_end) of the sequence    */
@@ -68,17 +61,16 @@ struct q3_schedule {
     uint32_t tokens = 0, n_kv_heads = 0, shared_len = 0, n_shared_pages = 0;
     std::vector<uint32_t> page_ids;       /* [shared | private tables]        */
     std::vector<uint32_t> row_tag, row_lp; /* per packed token                */
-    std::vector<uint32_t> tile_run_begin; /* [token tiles + 1]                */
     std::vector<q3_run> runs;
     std::vector<q3_segment> segments;
     std::vector<uint32_t> cta_seg_begin;  /* [grid + 1]                       */
-    std::vector<q3_merge_item> merges;
+    uint32_t n_cut_items = 0;             /* items split over several CTAs    */
     uint32_t grid = 0;
     uint32_t n_slots = 0;
     uint64_t total_key_tiles = 0;
 };
 
-/* Build runs, items, segments and the merge list.
+/* Build runs, items and segments.
  *   row_tag/row_lp   per token: branch handle and local position (a plain
  *                    causal sequence uses tag 0 and lp = absolute position)
  *   shared_pages     page ids of the shared prefix (ceil(shared_len/16))

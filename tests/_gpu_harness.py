@@ -46,7 +46,7 @@ def dev(a, dtype, device="cuda"):
 
 
 def run_case_native(pkg, case, out_fp32=False, prefill_chunks=None, permute_pages=True,
-                    layer=1, seed=0, return_runtime=False, device=0):
+                    layer=1, seed=0, return_runtime=False, device=0, sched_policy=None):
     """Prefix prefill (optionally in chunks) + packed suffix pass through the C
     ABI. Inputs are given as bf16. Returns the attention output [T,H,D] fp32."""
     P, S, T = case.P, case.S, case.T
@@ -61,6 +61,8 @@ def run_case_native(pkg, case, out_fp32=False, prefill_chunks=None, permute_page
                      num_pages=num_pages, out_fp32=out_fp32, rms_eps=case.eps,
                      rope_theta=case.theta, device=device)
     cuda = torch.device("cuda", device)
+    if sched_policy is not None:
+        rt.set_schedule_policy(sched_policy)
     rt.set_qk_norm(layer, case.q_norm_w, case.k_norm_w)
     odt = torch.float32 if out_fp32 else torch.bfloat16
     out = torch.zeros(T, case.H, case.D, dtype=odt, device=cuda)

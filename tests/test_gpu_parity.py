@@ -320,6 +320,10 @@ def test_bounded_wait_reports_instead_of_hanging(pkg):
         rt.synchronize()
     assert rt.stats().device_status & 2
     assert int(flags.sum().item()) == 5          # the device still answers
+    # the documented recovery: clear the status word and the arrival counters
+    rt.reset_status()
+    rt.synchronize()
+    assert rt.stats().device_status == 0
     rt.close()
 
 

@@ -50,6 +50,14 @@ def test_geometry_is_checked_before_any_cuda_call(pkg):
                     max_tokens=16, num_pages=8, head_dim=64)
 
 
+def test_decode_work_rejects_empty_context(pkg):
+    work, swb = pkg.decode_work_host(np.asarray([40, 3000], np.uint32))
+    assert len(work) == 1 + 3 and swb.tolist() == [0, 1, 4]
+    assert work[:, 3].tolist() == [0, 1, 2, 3]          # slot == index of the work item
+    with pytest.raises(pkg.Q3Error, match="no context"):
+        pkg.decode_work_host(np.asarray([40, 0], np.uint32))
+
+
 def test_pack_suffix_matches_reference_packing(pkg):
     # ref: src/q3_decide.cu:440-464 - tight packing, positions = P + j
     items = [(5, 3), (2, 1), (7, 4)]
@@ -112,7 +120,7 @@ def _check_schedule(pkg, row_tag, row_lp, n_kv, shared_len, ppb, nb, ctas, locks
             for p in parts:
                 assert p[2] >= 0 and p[2] not in slots
                 slots.add(p[2])
-    assert summ.n_merges == n_cut and summ.n_slots == len(slots)
+    assert summ.n_cut_items == n_cut and summ.n_slots == len(slots)
     loads = list(per_cta.values())
     assert len(loads) <= summ.grid == min(ctas, summ.total_key_tiles)
     if balanced and len(loads) == summ.grid:
@@ -138,7 +146,7 @@ def test_schedule_cascade_configs(pkg):
         # whole-item waves + stream-K tail: same coverage, same balance (equal items),
         # and no more cut items than CTAs
         s = _check_schedule(pkg, tag, lp, 8, P, (n + 15) // 16, B, 148, lockstep=True)
-        assert s.n_merges <= 148
+        assert s.n_cut_items <= 148
 
 
 def test_schedule_ragged_and_tiny(pkg):

@@ -1,5 +1,6 @@
 """The allocation-free decode entry point (q3_cuda_attention_decode_noalloc),
-called through the C ABI, against the ordinary decode entry point.
+called through the C ABI, against the ordinary decode entry point and against
+the CPU oracle.
 
 Who needs it: hosts that cannot call cudaMalloc when they need attention - a
 server whose arena owns the whole device heap, a process that forbids device
@@ -14,6 +15,7 @@ import pytest
 import torch
 
 import __graft_entry__ as entry
+import q3_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 ATOL = 2e-3
@@ -62,6 +64,20 @@ def test_noalloc_decode_matches_decode_entry_twice():
         torch.cuda.synchronize()
         err = (out.float() - ref.float()).abs().max().item()
         assert err <= ATOL, err
+        # no bounded wait of the call gave up (the word is read and cleared)
+        assert pkg.attention_decode_noalloc_status() == 0
+    # ... and against the oracle (ref math: src/q3_forward.cu:218-290), fed the
+    # f16 query and the f16 pages the kernel read
+    scale = np.float32(1 / np.sqrt(D))
+    qf = q_f16.float().cpu().numpy()
+    got = out.float().cpu().numpy()
+    for s, c in enumerate(ctx):
+        pages = torch.from_numpy(perm[indptr[s]:indptr[s + 1]].astype(np.int64)).cuda()
+        ks = kp[layer][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy()
+        vs = vp[layer][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy()
+        want = oracle.decode(qf[s], ks, vs, scale)
+        half_ulp = np.abs(want) * 2.0 ** -8          # bf16 output rounding
+        assert (np.maximum(np.abs(got[s] - want) - half_ulp, 0).max() <= ATOL), s
     assert torch.cuda.mem_get_info()[0] >= free_before - (1 << 20)
 
     # beyond the fixed scratch: refused with a clear message, nothing launched
