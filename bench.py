@@ -380,7 +380,6 @@ def case_prefill(pkg, torch, device, T=4096, reps=20):
     res = {"tokens": T, "ms": ms, "tflops": flops / ms / 1e9, "tokens_per_s": T / ms * 1e3,
            "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
            "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
-           "merge_ms": ph["merge"][0] / max(ph["merge"][1], 1),
            "kvwrite_ms": w_ms, "kvwrite_algorithmic_bytes": T * (H + 2 * HKV) * D * 2 * 2,
            "kvwrite_gbs": T * (H + 2 * HKV) * D * 2 * 2 / 1e6 / w_ms,
            "kvwrite_frac_of_hbm_peak": T * (H + 2 * HKV) * D * 2 * 2 / 1e6 / w_ms / peaks["hbm_gbs"]}
@@ -416,7 +415,6 @@ def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20, n_kv_heads=HKV
            "suffix_tokens_per_s": S / ms * 1e3, "tflops": flops / ms / 1e9,
            "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
            "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
-           "merge_ms": ph["merge"][0] / max(ph["merge"][1], 1),
            "kvwrite_ms": ph["kvwrite"][0] / max(ph["kvwrite"][1], 1)}
     for o in (plan, bset, prefix):
         o.close()

@@ -13,21 +13,30 @@
  * Shape of the computation (per CTA, persistent over its schedule segments):
  *   M tile   128 rows = 16 query tokens x the 8 query heads of one KV head
  *            (GQA packing: the 8 heads share every K/V tile). Two M tiles per
- *            CTA (32 tokens) ping-pong so one tile's softmax overlaps the
- *            other's MMAs.
+ *            CTA (32 tokens) share every K/V tile in shared memory.
  *   S = Q K^T   tcgen05.mma kind::f16, A = Q (smem, K-major, 128B swizzle),
  *               B = K pages (smem, K-major), D = S in tensor memory (fp32).
- *   softmax     one thread per row reads its S row with tcgen05.ld, keeps the
- *               running max / sum in registers, writes P as f16 back into the
- *               S columns (tcgen05.st).
+ *               ONE S buffer serves both M tiles in turn: a softmax thread
+ *               moves its S row into registers (tcgen05.ld) and hands the
+ *               buffer back at once, so the other M tile's S - and this M
+ *               tile's S of the next key tile - are computed while it
+ *               exponentiates. (M = 128, N = 64 MMAs, which would allow two
+ *               half-width S buffers per M tile, run at 55 instead of 32
+ *               clocks on this part: shared-memory bound.)
+ *   softmax     one thread per row: running max / sum in registers, P written
+ *               as f16 into a P buffer of its own M tile (tcgen05.st), in two
+ *               halves of 64 keys so that PV starts early.
  *   O += P V    tcgen05.mma, A = P from tensor memory, B = V pages (smem,
  *               MN-major), D = O in tensor memory (fp32).
+ *   TMEM        S [0,128), P0 [128,192), P1 [192,256), O0 [256,384), O1 [384,512).
  *   K/V pages   4 KiB per page per head, fetched by TMA (two 64-column boxes,
  *               128-byte swizzle) straight into the UMMA operand layout. Every
  *               CTA issues its own loads, from this GPU's memory only.
- * Warp roles: 0 = TMA producer, 1 = MMA issuer (owns the TMEM allocation),
- * 2-3 idle (register reallocation works on groups of 4 warps), 4-7 = softmax
- * of M tile 0, 8-11 = softmax of M tile 1.
+ * Warp roles: 0 = TMA producer, 1 = issuer of the S MMAs (owns the TMEM
+ * allocation), 2 / 3 = issuers of the PV MMAs of M tile 0 / 1 (three threads
+ * issue, each waiting on its own events in order, so that no event waits
+ * behind an unrelated one), 4-7 = softmax of M tile 0, 8-11 = softmax of M
+ * tile 1.
  *
  * Work is cut stream-K style on the host (q3_sched.h): a CTA receives
  * segments (item, key-tile range). A segment that covers its whole item
@@ -35,12 +44,11 @@
  * partials plus (max, sum) and bumps an arrival counter per 32 rows; the warp
  * that arrives last combines all pieces of its rows with log-sum-exp (its own
  * partial straight from tensor memory) and writes them. No CTA waits for
- * another. In head-sharded runs the rows are also stored
- * into the other GPUs' gathered buffers (peer memory), so the per-layer
- * all-gather is part of this kernel.
+ * another.
  *
  * Every mbarrier wait is bounded; on expiry the thread raises a flag in shared
- * memory, the status word is set and all roles drain and leave.
+ * memory, the status word is set and all roles leave; the producer first
+ * waits (bounded) for the loads it still has in flight.
  *
  * Algorithmic cost: 4*128 FLOP per (query head row, visible key) pair; bytes
  * = Q in + O out + each distinct K/V page once.
@@ -70,11 +78,14 @@ constexpr uint32_t kSlotInvalid = 0, kSlotShared = 1, kSlotPrivate = 2;
 constexpr uint32_t kNoTag = 0xFFFFFFFEu;
 
 /* TMEM columns */
-constexpr uint32_t kColS = 0;            /* S_q at kColS + q*128; P_q aliases its first 64 */
-constexpr uint32_t kColO = 256;          /* O_q at kColO + q*128 */
+constexpr uint32_t kColS = 0;            /* the one S buffer (fp32, 128 columns)          */
+constexpr uint32_t kColP = 128;          /* P_q (f16 pairs) at kColP + q*64               */
+constexpr uint32_t kColO = 256;          /* O_q at kColO + q*128                          */
 
 /* lazy rescale threshold in log2 units (P stays <= 2^8, exact enough in f16) */
 constexpr float kTau = 8.0f;
+/* polls granted to the drain of in-flight loads on the abort path */
+constexpr uint32_t kDrainPolls = 1u << 16;
 
 struct TileMeta {
     uint32_t nomask;
@@ -88,7 +99,10 @@ struct Barriers {
     uint64_t q_full, q_empty;
     uint64_t k_full[kStages], k_empty[kStages];
     uint64_t v_full[kStages], v_empty[kStages];
-    uint64_t s_full[kNQ], p_half[kNQ][2], o_full[kNQ];
+    uint64_t s_full[kNQ];        /* S of M tile q is complete (tcgen05.commit)            */
+    uint64_t s_free;             /* 128 softmax threads moved their S row into registers  */
+    uint64_t p_half[kNQ][2];     /* 128 threads stored P for keys [64h, 64h+64)           */
+    uint64_t pv_done[kNQ][2];    /* the PV MMAs of that half are complete                 */
 };
 
 struct Misc {
@@ -98,14 +112,6 @@ struct Misc {
     TileMeta meta[kMetaRing];
 };
 
-/* Head-sharded runs: the same output rows are also stored into the gathered
- * buffers of the other GPUs of the box (plain stores to peer-mapped memory
- * over NVLink), which makes the per-layer all-gather part of the epilogue
- * instead of a separate collective that would compete for SMs. */
-struct OutPeers {
-    void *ptr[Q3_MAX_GATHER_RANKS];
-    uint32_t n;
-};
 struct GatherFlags {
     uint32_t *ptr[Q3_MAX_GATHER_RANKS];
     uint32_t n;
@@ -128,7 +134,6 @@ struct AttnParams {
     float scale_log2;           /* scale * log2(e) */
     uint32_t out_fp32;
     void *out;                  /* [tokens][n_heads][128] bf16, or fp32 */
-    OutPeers peers;             /* extra destinations of every output row */
     float *part_o;
     float2 *part_ml;
     uint32_t *fix_counters;     /* [cut items][2 M tiles][4 row quarters] arrivals */
@@ -169,8 +174,9 @@ __device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
  * x = n + r, r in [-0.5, 0.5], cubic minimax for 2^r (relative error 7.5e-5,
  * below the f16 rounding of P), n added into the exponent field. The MUFU
  * executes 16 ex2 per clock per SM, exactly as many as the tensor core consumes
- * at full rate; moving a share of them to the FMA pipe takes it off the
- * critical path. Inputs must be finite and >= -126. */
+ * at full rate: with both pipes on the critical path, a share of the
+ * exponentials on the FMA pipe gives the MUFU slack. Inputs must be finite and
+ * >= -126. */
 __device__ __forceinline__ void exp2_poly2(uint64_t x2, float &p0, float &p1) {
     const uint64_t magic = pack2(12582912.0f, 12582912.0f);       /* 1.5 * 2^23 */
     const uint64_t neg_magic = pack2(-12582912.0f, -12582912.0f);
@@ -187,19 +193,15 @@ __device__ __forceinline__ void exp2_poly2(uint64_t x2, float &p0, float &p1) {
     p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(xr0) << 23));
     p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(xr1) << 23));
 }
-/* Pairs out of every 8 whose exponentials go through exp2_poly2. Measured on
- * B200 (one layer of the benchmark stack, TFLOP/s): 0 -> 1195, 1 -> 1177,
- * 2 -> 1170, 3 -> 1136: the loop is latency- and power-bound rather than
- * MUFU-throughput-bound, so the extra FMA-pipe instructions do not pay; the
- * path is kept for parts with a different balance. */
+/* Pairs out of every 8 whose exponentials go through exp2_poly2. */
 #ifndef Q3_POLY_PAIRS_OF_8
 #define Q3_POLY_PAIRS_OF_8 0
 #endif
 
 /* Register budget: setmaxnreg must be executed identically by all four warps
- * of a warp group. Warps 0-3 (producer, MMA issuer, two idle) give registers
- * back; the two softmax groups (one S row of 128 fp32 per thread) take them.
- * 384 threads x 168 at launch = 128 x 40 + 256 x 232. */
+ * of a warp group. Warps 0-3 (producer and the three MMA issuers) give
+ * registers back; the two softmax groups (one S row of 128 fp32 per thread)
+ * take them. 384 threads x 168 at launch = 128 x 40 + 256 x 232. */
 __device__ __forceinline__ void regs_release() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
 }
@@ -217,20 +219,20 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity,
     atomicExch(&misc->abort_flag, 1u);
     return false;
 }
+/* Abort path only: give a load that is still in flight time to land. */
+__device__ __forceinline__ void drain_wait(uint64_t *bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kDrainPolls; i++)
+        if (mbar_try_wait(bar, parity)) return;
+}
 
-/* Store 32 consecutive columns of one output row (already normalised) to the
- * local output and to every peer destination. */
+/* Store 32 consecutive columns of one output row (already normalised). */
 __device__ __forceinline__ void store_row_chunk(const AttnParams &p, size_t off,
                                                 const float *v) {
     if (p.out_fp32) {
 #pragma unroll
-        for (uint32_t i = 0; i < 8; i++) {
-            const float4 f = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
-            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + off + i * 4) = f;
-            for (uint32_t d = 0; d < p.peers.n; d++)
-                *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.peers.ptr[d]) + off +
-                                            i * 4) = f;
-        }
+        for (uint32_t i = 0; i < 8; i++)
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + off + i * 4) =
+                make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
     } else {
 #pragma unroll
         for (uint32_t i = 0; i < 4; i++) {
@@ -240,9 +242,6 @@ __device__ __forceinline__ void store_row_chunk(const AttnParams &p, size_t off,
             for (uint32_t e = 0; e < 4; e++)
                 h[e] = __floats2bfloat162_rn(v[i * 8 + 2 * e], v[i * 8 + 2 * e + 1]);
             *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + off + i * 8) = u;
-            for (uint32_t d = 0; d < p.peers.n; d++)
-                *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.peers.ptr[d]) +
-                                           off + i * 8) = u;
         }
     }
 }
@@ -265,13 +264,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             mbar_init(&bar.k_full[s], 1);
             mbar_init(&bar.k_empty[s], 1);
             mbar_init(&bar.v_full[s], 1);
-            mbar_init(&bar.v_empty[s], 1);
+            mbar_init(&bar.v_empty[s], kNQ);     /* one commit per PV issuer */
         }
+        mbar_init(&bar.s_free, 128);
         for (uint32_t q = 0; q < kNQ; q++) {
             mbar_init(&bar.s_full[q], 1);
-            mbar_init(&bar.p_half[q][0], 128);
-            mbar_init(&bar.p_half[q][1], 128);
-            mbar_init(&bar.o_full[q], 1);
+            for (uint32_t h = 0; h < 2; h++) {
+                mbar_init(&bar.p_half[q][h], 128);
+                mbar_init(&bar.pv_done[q][h], 1);
+            }
         }
         misc->abort_flag = 0;
         fence_mbar_init();
@@ -296,7 +297,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             prefetch_tmap(&k_map);
             prefetch_tmap(&v_map);
         }
-        uint32_t it = 0;
+        uint32_t it = 0;          /* K tiles armed so far */
+        uint32_t v_armed = 0;     /* V tiles armed so far */
+        uint32_t q_armed = 0;     /* Q loads armed so far */
         bool alive = true;
         for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
             const q3_segment seg = p.segments[si];
@@ -325,7 +328,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                     (int32_t)(seg.kv_head * Q3_G),
                                     (int32_t)(seg.tok0 + q * 16), &bar.q_full);
             }
-            for (uint32_t tile = seg.tile_begin; tile < seg.tile_end; tile++, it++) {
+            q_armed++;
+            for (uint32_t tile = seg.tile_begin; tile < seg.tile_end; tile++) {
                 const uint32_t stage = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
                 /* lanes 0..7 resolve one page slot each */
@@ -385,6 +389,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     tma_load_2d(dst, &k_map, 0, row, &bar.k_full[stage]);
                     tma_load_2d(dst + kHalfBytes, &k_map, 64, row, &bar.k_full[stage]);
                 }
+                it++;
                 alive = wait_or_abort(&bar.v_empty[stage], ph ^ 1u, misc);
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
@@ -395,103 +400,111 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     tma_load_2d(dst, &v_map, 0, row, &bar.v_full[stage]);
                     tma_load_2d(dst + kHalfBytes, &v_map, 64, row, &bar.v_full[stage]);
                 }
+                v_armed++;
             }
         }
-    } else if (warp == 1) {
-        /* ===================== MMA issuer ======================= */
-        if (elect_one()) {
-            constexpr uint32_t idesc_qk = umma_idesc_f16(128, 128, false);
-            constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, true);
-            const uint32_t q_addr = smem_u32(smem + kSmemQ);
-            const uint32_t k_addr = smem_u32(smem + kSmemK);
-            const uint32_t v_addr = smem_u32(smem + kSmemV);
-            uint32_t it = 0;
-            bool alive = true;
-
-            auto issue_s = [&](uint32_t q, uint32_t stage) {
-                /* S_q = Q_q K^T : 8 steps of K = 16 over head_dim = 128 */
-#pragma unroll
-                for (uint32_t ks = 0; ks < 8; ks++) {
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3u) * 32u;
-                    umma_ss(tmem + kColS + q * 128u,
-                            umma_desc(q_addr + q * kTileBytes + off, 16, 1024),
-                            umma_desc(k_addr + stage * kTileBytes + off, 16, 1024),
-                            idesc_qk, ks > 0);
+        if (!alive && lane == 0) {
+            /* leaving early: the loads armed last may still be writing shared
+             * memory; wait for them (bounded) before the CTA can exit */
+            if (q_armed) drain_wait(&bar.q_full, (q_armed - 1) & 1u);
+            for (uint32_t b = 0; b < kStages; b++) {
+                if (it > b) {
+                    const uint32_t i = it - 1 - b;
+                    drain_wait(&bar.k_full[i % kStages], (i / kStages) & 1u);
                 }
-                umma_commit(&bar.s_full[q]);
-            };
-            auto issue_pv = [&](uint32_t q, uint32_t stage, bool accumulate, uint32_t half) {
-                /* O_q += P_q V for keys [64*half, 64*half+64): 4 steps of K = 16
-                 * keys; V is MN-major (64-column blocks 16 KiB apart, 8-key groups
-                 * 1 KiB apart). P arrives in two halves so that the first half's
-                 * MMAs overlap the second half's exponentials. */
-#pragma unroll
-                for (uint32_t ks = half * 4; ks < half * 4 + 4; ks++)
-                    umma_ts(tmem + kColO + q * 128u, tmem + kColS + q * 128u + ks * 8u,
-                            umma_desc(v_addr + stage * kTileBytes + ks * 2048u, kHalfBytes,
-                                      1024),
-                            idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
-                if (half == 1) umma_commit(&bar.o_full[q]);
-            };
-
-            for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
-                const q3_segment seg = p.segments[si];
-                const uint32_t n = seg.tile_end - seg.tile_begin;
-                alive = wait_or_abort(&bar.q_full, (si - seg_begin) & 1u, misc);
-                if (!alive) break;
-                /* S of the segment's first tile */
-                {
-                    const uint32_t stage = it % kStages;
-                    alive = wait_or_abort(&bar.k_full[stage], (it / kStages) & 1u, misc);
-                    if (!alive) break;
-                    tc_fence_after();
-                    issue_s(0, stage);
-                    issue_s(1, stage);
-                    umma_commit(&bar.k_empty[stage]);
-                    if (n == 1) umma_commit(&bar.q_empty);
-                }
-                for (uint32_t j = 0; j < n && alive; j++, it++) {
-                    const uint32_t stage = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1u;
-                    const uint32_t nstage = (it + 1) % kStages;
-                    const uint32_t nph = ((it + 1) / kStages) & 1u;
-                    const bool more = j + 1 < n;
-                    for (uint32_t q = 0; q < kNQ && alive; q++) {
-                        alive = wait_or_abort(&bar.p_half[q][0], it & 1u, misc);
-                        if (alive && q == 0)
-                            alive = wait_or_abort(&bar.v_full[stage], ph, misc);
-                        if (!alive) break;
-                        tc_fence_after();
-                        issue_pv(q, stage, j > 0, 0);
-                        alive = wait_or_abort(&bar.p_half[q][1], it & 1u, misc);
-                        if (!alive) break;
-                        tc_fence_after();
-                        issue_pv(q, stage, j > 0, 1);
-                        if (q == kNQ - 1) umma_commit(&bar.v_empty[stage]);
-                        if (more) {
-                            if (q == 0) {
-                                alive = wait_or_abort(&bar.k_full[nstage], nph, misc);
-                                if (!alive) break;
-                                tc_fence_after();
-                            }
-                            issue_s(q, nstage);
-                            if (q == kNQ - 1) {
-                                umma_commit(&bar.k_empty[nstage]);
-                                if (j + 2 == n) umma_commit(&bar.q_empty);
-                            }
-                        }
-                    }
+                if (v_armed > b) {
+                    const uint32_t i = v_armed - 1 - b;
+                    drain_wait(&bar.v_full[i % kStages], (i / kStages) & 1u);
                 }
             }
         }
         __syncwarp();
-    } else if (warp >= 4) {
+    } else if (warp == 1) {
+        /* ===================== issuer of S = Q K^T =====================
+         * One S buffer, used by the two M tiles in turn: S number g = 2*it + q
+         * may be issued once the softmax threads of S number g-1 have moved
+         * their rows into registers. */
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = umma_idesc_f16(128, 128, false);
+            const uint32_t q_addr = smem_u32(smem + kSmemQ);
+            const uint32_t k_addr = smem_u32(smem + kSmemK);
+            uint32_t it = 0;
+            bool alive = true;
+            for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
+                const q3_segment seg = p.segments[si];
+                const uint32_t n = seg.tile_end - seg.tile_begin;
+                alive = wait_or_abort(&bar.q_full, (si - seg_begin) & 1u, misc);
+                for (uint32_t j = 0; j < n && alive; j++, it++) {
+                    const uint32_t stage = it % kStages;
+                    for (uint32_t q = 0; q < kNQ && alive; q++) {
+                        const uint32_t g = 2u * it + q;
+                        if (g > 0) alive = wait_or_abort(&bar.s_free, (g - 1u) & 1u, misc);
+                        if (alive && q == 0)
+                            alive = wait_or_abort(&bar.k_full[stage], (it / kStages) & 1u, misc);
+                        if (!alive) break;
+                        tc_fence_after();
+                        /* 8 steps of K = 16 over head_dim = 128 */
+#pragma unroll
+                        for (uint32_t ks = 0; ks < 8; ks++) {
+                            const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3u) * 32u;
+                            umma_ss(tmem + kColS,
+                                    umma_desc(q_addr + q * kTileBytes + off, 16, 1024),
+                                    umma_desc(k_addr + stage * kTileBytes + off, 16, 1024),
+                                    idesc_qk, ks > 0);
+                        }
+                        umma_commit(&bar.s_full[q]);
+                    }
+                    if (!alive) break;
+                    umma_commit(&bar.k_empty[stage]);
+                    if (j + 1 == n) umma_commit(&bar.q_empty);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 4) {
+        /* ===================== issuers of O_q += P_q V =================== */
+        if (elect_one()) {
+            const uint32_t q = warp - 2u;
+            constexpr uint32_t idesc_pv = umma_idesc_f16(128, 128, true);
+            const uint32_t v_addr = smem_u32(smem + kSmemV);
+            uint32_t it = 0;
+            bool alive = true;
+            for (uint32_t si = seg_begin; si < seg_end && alive; si++) {
+                const q3_segment seg = p.segments[si];
+                const uint32_t n = seg.tile_end - seg.tile_begin;
+                for (uint32_t j = 0; j < n && alive; j++, it++) {
+                    const uint32_t stage = it % kStages;
+                    for (uint32_t half = 0; half < 2 && alive; half++) {
+                        alive = wait_or_abort(&bar.p_half[q][half], it & 1u, misc);
+                        if (alive && half == 0)
+                            alive = wait_or_abort(&bar.v_full[stage], (it / kStages) & 1u, misc);
+                        if (!alive) break;
+                        tc_fence_after();
+                        /* keys [64*half, 64*half+64): 4 steps of K = 16 keys; V is
+                         * MN-major (64-column blocks 16 KiB apart, 16-key groups
+                         * 2 KiB apart) */
+#pragma unroll
+                        for (uint32_t ks = half * 4; ks < half * 4 + 4; ks++)
+                            umma_ts(tmem + kColO + q * 128u, tmem + kColP + q * 64u + ks * 8u,
+                                    umma_desc(v_addr + stage * kTileBytes + ks * 2048u,
+                                              kHalfBytes, 1024),
+                                    idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(&bar.pv_done[q][half]);
+                    }
+                    if (!alive) break;
+                    umma_commit(&bar.v_empty[stage]);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
         /* ===================== softmax groups ==================== */
         regs_take();
         const uint32_t q = (warp - 4) >> 2;                 /* M tile of this group */
         const uint32_t row = (warp & 3u) * 32u + lane;       /* TMEM lane == tile row */
         const uint32_t lane_addr = ((warp & 3u) * 32u) << 16;
-        const uint32_t s_addr = tmem + lane_addr + kColS + q * 128u;
+        const uint32_t s_addr = tmem + lane_addr + kColS;
+        const uint32_t p_addr = tmem + lane_addr + kColP + q * 64u;
         const uint32_t o_addr = tmem + lane_addr + kColO + q * 128u;
         const float c = p.scale_log2;
         const float tau_raw = kTau / c;
@@ -510,8 +523,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
 
             for (uint32_t j = 0; j < n && alive; j++, it++) {
                 alive = wait_or_abort(&bar.s_full[q], it & 1u, misc);
-                if (alive && j > 0)
-                    alive = wait_or_abort(&bar.o_full[q], (it - 1) & 1u, misc);
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 tc_fence_after();
@@ -520,6 +531,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 for (uint32_t ch = 0; ch < 4; ch++)
                     tmem_ld32(s_addr + ch * 32u, reinterpret_cast<uint32_t *>(s) + ch * 32u);
                 tmem_wait_ld();
+                /* the row is in registers: the S buffer may be overwritten */
+                tc_fence_before();
+                mbar_arrive(&bar.s_free);
                 const TileMeta &m = misc->meta[it % kMetaRing];
                 if (!m.nomask) {
 #pragma unroll
@@ -558,7 +572,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 } else {
                     const bool need = mx > m_ref + tau_raw;
                     if (__any_sync(0xffffffffu, need)) {
-                        /* O_q was last written by PV(j-1), complete (o_full). */
+                        /* O_q must be at rest: the PV of the previous key tile done */
+                        alive = wait_or_abort(&bar.pv_done[q][1], (it - 1u) & 1u, misc);
+                        alive = __all_sync(0xffffffffu, alive);
+                        if (!alive) break;
+                        tc_fence_after();
                         const float f = need ? fast_exp2((m_ref - mx) * c) : 1.0f;
                         if (need) m_ref = mx;
                         l *= f;
@@ -583,11 +601,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
 #pragma unroll
                     for (uint32_t i = 0; i < 64; i++) {
                         if (i == 32) {
-                            /* keys 0..63 are ready: let their PV steps start */
-                            tmem_st32(s_addr, pk);
-                            tmem_wait_st();
-                            tc_fence_before();
-                            mbar_arrive(&bar.p_half[q][0]);
+                            /* keys 0..63 are ready. The P buffer still feeds the
+                             * previous key tile's PV until pv_done says otherwise. */
+                            if (it > 0) {
+                                alive = wait_or_abort(&bar.pv_done[q][0], (it - 1u) & 1u, misc);
+                                alive = __all_sync(0xffffffffu, alive);
+                            }
+                            if (alive) {
+                                tc_fence_after();
+                                tmem_st32(p_addr, pk);
+                                tmem_wait_st();
+                                tc_fence_before();
+                                mbar_arrive(&bar.p_half[q][0]);
+                            }
                         }
                         float x0, x1, p0, p1;
                         const uint64_t x2 = ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, neg2);
@@ -606,14 +632,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     unpack2(fadd2(fadd2(acc[0], acc[1]), fadd2(acc[2], acc[3])), a0, a1);
                     l += a0 + a1;
                 }
-                tmem_st32(s_addr + 32u, pk + 32);
+                if (!alive) break;
+                if (it > 0) {
+                    alive = wait_or_abort(&bar.pv_done[q][1], (it - 1u) & 1u, misc);
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+                }
+                tc_fence_after();
+                tmem_st32(p_addr + 32u, pk + 32);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bar.p_half[q][1]);
             }
             if (!alive) break;
-            /* ---- segment epilogue: O_q of the last tile ---- */
-            alive = wait_or_abort(&bar.o_full[q], (it - 1) & 1u, misc);
+            /* ---- segment epilogue: O_q after the last key tile ---- */
+            alive = wait_or_abort(&bar.pv_done[q][1], (it - 1u) & 1u, misc);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) break;
             tc_fence_after();
@@ -721,7 +754,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     }
                 }
             }
-            /* the next segment's first PV overwrites O_q only after p_full of
+            /* the next segment's first PV overwrites O_q only after p_half of
              * its first tile, which this thread raises after these loads */
             tc_fence_before();
         }
@@ -813,8 +846,7 @@ bool q3_prepare_attention_kernel(char *error, size_t error_len) {
 }
 
 bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st,
-                         void *out_bf16, const q3_gather_peers *gather, char *error,
-                         size_t error_len) {
+                         void *out_bf16, char *error, size_t error_len) {
     const q3_attn_config &c = rt->cfg;
     CUtensorMap q_map;
     if (!q3_encode_tmap_q(&q_map, rt->q2, c.n_heads, st->tokens, error, error_len))
@@ -836,16 +868,6 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st
     p.scale_log2 = (1.0f / sqrtf((float)Q3_D)) * 1.4426950408889634f;
     p.out_fp32 = c.out_fp32;
     p.out = out_bf16;
-    p.peers.n = 0;
-    if (gather) {
-        /* rows of this rank go to slot `rank` of every OTHER rank's gathered
-         * buffer; the local slot is `out_bf16` itself */
-        const size_t slot_bytes = (size_t)st->tokens * c.n_heads * Q3_D * (c.out_fp32 ? 4 : 2);
-        for (uint32_t d = 0; d < gather->n_ranks; d++)
-            if (d != gather->rank)
-                p.peers.ptr[p.peers.n++] =
-                    (uint8_t *)gather->gathered[d] + slot_bytes * gather->rank;
-    }
     p.part_o = rt->part_o;
     p.part_ml = rt->part_ml;
     p.fix_counters = rt->fix_counters;

@@ -221,8 +221,7 @@ bool q3_launch_kvwrite(q3_attn_runtime *rt, uint32_t layer, const void *q,
                        const uint32_t *dst_slot, void *q_out, char *error,
                        size_t error_len);
 bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer,
-                         const q3_stage *st, void *out_bf16,
-                         const q3_gather_peers *gather, char *error,
+                         const q3_stage *st, void *out_bf16, char *error,
                          size_t error_len);
 bool q3_launch_gather_signal(q3_attn_runtime *rt, const q3_gather_peers *g, uint32_t seq,
                              cudaStream_t stream, char *error, size_t error_len);

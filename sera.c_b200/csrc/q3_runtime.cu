@@ -692,7 +692,7 @@ extern "C" bool q3_prefix_prefill_layer(q3_prefix_kv *prefix, uint32_t layer,
     if (!q3_launch_kvwrite(rt, layer, q, k, v, tokens, st->rope_pos, st->dst_page,
                            st->dst_slot, rt->q2, error, error_len))
         return false;
-    return q3_launch_attention(rt, layer, st, out, NULL, error, error_len);
+    return q3_launch_attention(rt, layer, st, out, error, error_len);
 }
 
 extern "C" bool q3_prefix_advance(q3_prefix_kv *prefix, uint32_t tokens,
@@ -1032,7 +1032,7 @@ extern "C" bool q3_suffix_attention_layer(q3_pack_plan *plan, uint32_t layer,
     if (!q3_launch_kvwrite(rt, layer, q, k, v, plan->tokens, st->rope_pos, st->dst_page,
                            st->dst_slot, rt->q2, error, error_len))
         return false;
-    return q3_launch_attention(rt, layer, st, out, NULL, error, error_len);
+    return q3_launch_attention(rt, layer, st, out, error, error_len);
 }
 
 extern "C" bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t layer,
@@ -1065,11 +1065,11 @@ extern "C" bool q3_suffix_attention_layer_gathered(q3_pack_plan *plan, uint32_t 
     /* The kernels write this rank's slot of its own gathered buffer. The copies
      * to the other ranks go through the copy engines on a side stream (NVLink,
      * no SM involved), overlapped with the next layer's kernels; the flags are
-     * published after them on the same stream. (The kernels can also store the
-     * rows into peer memory themselves - q3_launch_attention takes the peer
-     * list - but scattered 16-byte remote stores from the softmax warps
-     * stalled them: 450 us instead of 250 us per layer at 8 GPUs.) */
-    if (!q3_launch_attention(rt, layer, st, local, NULL, error, error_len)) return false;
+     * published after them on the same stream. (Storing the rows into peer
+     * memory from the attention epilogue was measured and dropped: scattered
+     * 16-byte remote stores stalled the softmax warps, 450 us instead of 250 us
+     * per layer at 8 GPUs.) */
+    if (!q3_launch_attention(rt, layer, st, local, error, error_len)) return false;
     if (!rt->gather_ready) {
         bool ok = cudaStreamCreateWithFlags(&rt->gather_stream, cudaStreamNonBlocking) ==
                   cudaSuccess;

@@ -155,8 +155,10 @@ def test_decode_256_sequences_full_size(pkg):
         c = int(ctx[s])
         pages = torch.from_numpy(perm[indptr[s]:indptr[s + 1]].astype(np.int64)).cuda()
         # pool layout [Hkv, page, 16, D] -> [tokens, Hkv, D]
-        ks = kp[0][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy()
-        vs = vp[0][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy()
+        ks = np.ascontiguousarray(
+            kp[0][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy())
+        vs = np.ascontiguousarray(
+            vp[0][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy())
         ref = oracle.decode(qn[s], ks, vs, scale)
         err = float(np.abs(got[s] - ref).max())
         worst = max(worst, err)

@@ -73,9 +73,11 @@ def test_noalloc_decode_matches_decode_entry_twice():
     got = out.float().cpu().numpy()
     for s, c in enumerate(ctx):
         pages = torch.from_numpy(perm[indptr[s]:indptr[s + 1]].astype(np.int64)).cuda()
-        ks = kp[layer][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy()
-        vs = vp[layer][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy()
-        want = oracle.decode(qf[s], ks, vs, scale)
+        ks = np.ascontiguousarray(
+            kp[layer][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy())
+        vs = np.ascontiguousarray(
+            vp[layer][:, pages].permute(1, 2, 0, 3).reshape(-1, Hkv, D)[:c].float().cpu().numpy())
+        want = oracle.decode(np.ascontiguousarray(qf[s]), ks, vs, scale)
         half_ulp = np.abs(want) * 2.0 ** -8          # bf16 output rounding
         assert (np.maximum(np.abs(got[s] - want) - half_ulp, 0).max() <= ATOL), s
     assert torch.cuda.mem_get_info()[0] >= free_before - (1 << 20)
