@@ -11,14 +11,18 @@ seeded bf16 N(0,1) (seed = layer index). One step = all 64 layers: fused
 QK-RMSNorm + RoPE + KV write of the suffix tokens, then shared-prefix +
 own-suffix attention. With N GPUs the KV heads are sharded (8/N KV heads and
 their 64/N query heads per rank) and the per-head outputs are all-gathered
-after every layer (NCCL, overlapped with the next layer).
+after every layer (copy-engine copies into peer-mapped buffers plus flags,
+overlapped with the next layer; --gather nccl keeps the NCCL baseline).
 
 value      suffix tokens per second through the 64-layer stack, inputs resident
            in HBM, device-timed (CUDA events on the launching stream), max over
            ranks.
 e2e        the same through the host-buffer C-ABI entry: per layer, q/k/v come
            from pinned host memory and the output goes back to pinned host
-           memory, copies inside the timed region.
+           memory, copies (and at N > 1 the exchange) inside the timed region.
+parity_check  after the timed region: rows of the last layer against the CPU
+           oracle (at N > 1: every rank's gathered buffer); the run fails when
+           it does.
 roofline   the tensor-core attention kernel: algorithmic FLOPs per launch
            (4*128 per query-head row and visible key) / its mean device time,
            against the measured bf16 peak of MEASURED_PEAKS.json.
@@ -49,9 +53,10 @@ UNIT = "tokens/s"
 PAIRS_PER_HEAD = TOKENS * PREFIX + BRANCHES * (SUFFIX * (SUFFIX + 1) // 2)
 FLOPS_PER_LAYER = 4 * D * H * PAIRS_PER_HEAD
 FLOPS_PER_STEP = FLOPS_PER_LAYER * L
-# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at N = 1, from the
-# ncu capture summarised in profiles/attention_tc_kernel__stack_layer_p32768_b128x16.md
-# (205.8 MB read + 49.9 MB written; algorithmic bytes 218 MB). Scales with 1/N.
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at N = 1, from an
+# ncu capture of `--case stack_layer_p32768_b128x16` (205.8 MB read + 49.9 MB written;
+# algorithmic bytes 218 MB). A constant, not re-measured per run; at N > 1 the per-rank
+# share (1/N of the KV heads) is reported and marked as scaled.
 ATTENTION_DRAM_BYTES_PER_LAUNCH = 255.6e6
 
 
@@ -186,17 +191,18 @@ def run_ours(args):
     out_host = torch.zeros(TOKENS, hq, D, dtype=torch.bfloat16).pin_memory()
     stream = rt.torch_stream()
 
-    fused = world > 1 and args.gather == "fused"
+    fused = world > 1 and args.gather == "copy"
     pg = sharding.PeerGather(TOKENS, hq, D, torch.bfloat16, device) if fused else None
 
     def step_device():
         if fused:
-            # attention kernels store their rows into every rank's gathered
-            # buffer; buffer b is reused by layer l+2 only after every rank
-            # has seen layer l complete (device-side flag wait, no collective)
-            # sequence numbers are step-relative; the device-side counter
-            # advanced at the end makes every step (or graph replay) publish
-            # fresh ones
+            # each layer writes this rank's slot of its gathered buffer; copy
+            # engines push the slot to the other ranks on a side stream and
+            # publish flags; buffer b is reused by layer l+2 only after every
+            # rank's layer-l rows have arrived here (device-side flag wait, no
+            # collective). Sequence numbers are step-relative; the device-side
+            # counter advanced at the end makes every step (or graph replay)
+            # publish fresh ones
             for l in range(L):
                 if l >= 2:
                     rt.wait_gathered(pg.peers(l), l - 1)
@@ -218,6 +224,18 @@ def run_ours(args):
                 w.wait()
 
     def step_host():
+        if fused:
+            # the whole step as a host caller sees it: host buffers in, the
+            # exchange between the ranks, this rank's rows back to the host
+            for l in range(L):
+                if l >= 2:
+                    rt.wait_gathered(pg.peers(l), l - 1)
+                plan.attention_layer_gathered_host(l, hq_[l], hk_[l], hv_[l], pg.peers(l),
+                                                   l + 1, out_host)
+            rt.wait_gathered(pg.peers(L - 2), L - 1)
+            rt.wait_gathered(pg.peers(L - 1), L)
+            rt.gather_advance(L)
+            return
         for l in range(L):
             plan.attention_layer_host(l, hq_[l], hk_[l], hv_[l], out_host)
 
@@ -259,7 +277,7 @@ def run_ours(args):
         sampler.start()
     use_graph = args.graph == "on" or (args.graph == "auto" and fused)
     if use_graph and world > 1 and args.gather == "nccl":
-        raise SystemExit("--graph on records this library's calls only: use --gather fused|none")
+        raise SystemExit("--graph on records this library's calls only: use --gather copy|none")
     if use_graph:
         # the 64-layer step recorded once and replayed as one graph launch;
         # per-kernel times then come from a short eager pass after the timed region
@@ -278,10 +296,19 @@ def run_ours(args):
     else:
         ms, phases, launches = timed(step_device, args.steps, args.warmup)
         clocks = sampler.stop() if sampler else None
-    ms_e2e, _, _ = timed(step_host, max(1, min(args.steps, 3)), 1, drain=rt.synchronize)
-    e2e_steps = max(1, min(args.steps, 3))
+    ms_e2e, _, _ = timed(step_host, args.steps, args.warmup, drain=rt.synchronize)
+    e2e_steps = args.steps
     rt.synchronize()
     status = rt.stats().device_status
+    parity = parity_check(torch, dist, pkg, rt, plan, pg, kp, vp, perm[:n_prefix_pages],
+                          dq_[L - 1], dk_[L - 1], dv_[L - 1], rank, world, device, stream)
+    if world > 1:
+        flag = torch.tensor([1.0 if parity["ok"] else 0.0], dtype=torch.float64, device=device)
+        worst = torch.tensor([parity["max_normalised"]], dtype=torch.float64, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        parity["ok"] = bool(flag.item() > 0.5)
+        parity["max_normalised"] = float(worst.item())
 
     result = None
     if rank == 0:
@@ -318,11 +345,14 @@ def run_ours(args):
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
                          "traffic": ATTENTION_DRAM_BYTES_PER_LAUNCH / n_gpus,
-                         "traffic_unit": "bytes per launch (ncu capture, see profiles/)",
+                         "traffic_unit": "bytes per launch: one ncu capture at N = 1"
+                                         + (", scaled by 1/N (not re-measured)" if n_gpus > 1 else ""),
                          "peak_source": "%s bf16 sustained" % peaks["source"],
                          "ms_per_launch": per_launch_ms, "launches": attn_n,
                          "flops_per_launch": flops_per_launch},
             "kernel_ms_per_step": {k: v[0] / args.steps for k, v in phases.items()},
+            "exposed_exchange_ms_per_step": phases["gather_wait"][0] / args.steps,
+            "parity_check": parity,
             "launch_mode": ("one CUDA graph per step; per-kernel times from an eager pass "
                             "of the same step after the timed region") if use_graph
                            else "eager; per-kernel times from the timed region",
@@ -342,6 +372,72 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit("parity_check failed: %s" % json.dumps(parity))
+
+
+def parity_check(torch, dist, pkg, rt, plan, pg, kp, vp, prefix_pages, q, k, v, rank,
+                 world, device, stream):
+    """Outside the timed region: the last layer once more, a handful of its rows
+    against the CPU oracle (ref math: src/q3_forward.cu:418-525). At N > 1 every
+    rank compares ALL ranks' rows as they arrived in its gathered buffer with
+    the oracle rows computed by their owners, so the exchange is checked too.
+    Error measure: |got - oracle| less half a bf16 ulp of the oracle value
+    (output rounding), absolute and normalised by max |oracle|; both <= 2e-3."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import q3_oracle as oracle
+    layer = L - 1
+    toks = [0, 15, 16, 31, TOKENS // 2 + 5, TOKENS - 17, TOKENS - 1]
+    hq, hk = q.shape[1], k.shape[1]
+    with torch.cuda.stream(stream):
+        torch.cuda.synchronize()
+        if pg is not None:
+            dist.barrier()
+            plan.attention_layer_gathered(layer, q, k, v, pg.peers(0), 1)
+            rt.wait_gathered(pg.peers(0), 1)
+            rt.gather_advance(1)
+            rt.synchronize()
+            dist.barrier()
+            got = pg.bufs[0][:, toks].float().cpu().numpy()          # [world, n, hq, D]
+        else:
+            out = torch.zeros(TOKENS, hq, D, dtype=torch.bfloat16, device=device)
+            plan.attention_layer(layer, q, k, v, out)
+            rt.synchronize()
+            got = out[toks].float().cpu().numpy()[None]
+    idx = torch.from_numpy(prefix_pages.astype(np.int64)).to(device)
+    kpre = np.ascontiguousarray(kp[layer][:, idx].permute(1, 2, 0, 3).reshape(PREFIX, hk, D)
+                                .float().cpu().numpy())
+    vpre = np.ascontiguousarray(vp[layer][:, idx].permute(1, 2, 0, 3).reshape(PREFIX, hk, D)
+                                .float().cpu().numpy())
+    ones = np.ones(D, np.float32)
+    pos = (PREFIX + np.tile(np.arange(SUFFIX), BRANCHES)).astype(np.uint32)
+    qn = oracle.rms_norm(q.float().cpu().numpy(), ones, 1e-6)
+    kn = oracle.rms_norm(k.float().cpu().numpy(), ones, 1e-6)
+    qn, kn = oracle.rope(qn, kn, 0, pos, oracle.inv_freq(1e6, D))
+    vn = v.float().cpu().numpy()
+    scale = np.float32(1 / np.sqrt(D))
+    ref = np.zeros((len(toks), hq, D), np.float32)
+    for i, t in enumerate(toks):
+        b, lp = t // SUFFIX, t % SUFFIX
+        keys = np.concatenate([kpre, kn[b * SUFFIX:b * SUFFIX + lp + 1]])
+        vals = np.concatenate([vpre, vn[b * SUFFIX:b * SUFFIX + lp + 1]])
+        ref[i] = oracle.attention(np.ascontiguousarray(qn[t:t + 1]), keys, vals, PREFIX + lp,
+                                  PREFIX + lp + 1, scale)[0]
+    if world > 1 and pg is not None:
+        mine = torch.from_numpy(ref).to(device)
+        allref = torch.zeros((world,) + ref.shape, dtype=torch.float32, device=device)
+        dist.all_gather_into_tensor(allref.view(-1), mine.view(-1))
+        ref_all = allref.cpu().numpy()
+    else:
+        ref_all = ref[None]
+    r64 = ref_all.astype(np.float64)
+    e = np.maximum(np.abs(got.astype(np.float64) - r64) - np.abs(r64) * 2.0 ** -8, 0.0)
+    max_abs, norm = float(e.max()), float(e.max() / np.abs(r64).max())
+    ok = bool(np.isfinite(got).all() and max_abs <= 2e-3 and norm <= 2e-3)
+    return {"layer": layer, "rows": int(got.shape[0] * got.shape[1] * got.shape[2]),
+            "tokens": toks, "ranks_checked": int(got.shape[0]), "max_abs": max_abs,
+            "max_normalised": norm, "tolerance": 2e-3,
+            "against": "CPU oracle of the reference kernels, same bf16/f16 inputs", "ok": ok}
 
 
 def _time_calls(torch, rt, fn, reps, warmup=3):
@@ -607,13 +703,23 @@ def run_case(args):
     print(json.dumps({"case": args.case, **CASES[args.case](pkg, torch, device, args.reps)}))
 
 
+def host_cores():
+    """Host threads this process may use (its CPU affinity, else the core count)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_sample(n_branches, threads=None):
     """One layer of the workload restricted to `n_branches` branches (16 tokens
-    each, full 32768-token prefix) through the CPU oracle. Returns seconds."""
+    each, full 32768-token prefix) through the CPU oracle. Returns seconds.
+    The thread count is always set explicitly: a launcher that exports
+    OMP_NUM_THREADS=1 (torch.distributed.run does) must not turn the CPU arm
+    into a one-core run."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import q3_oracle as oracle
-    if threads:
-        oracle.set_threads(threads)
+    oracle.set_threads(threads or host_cores())
     rng = np.random.default_rng(0)
     S = n_branches * SUFFIX
     q = rng.standard_normal((S, H, D), dtype=np.float32)
@@ -779,7 +885,7 @@ def python_path_baseline():
         from transformers.models.qwen3.configuration_qwen3 import Qwen3Config
     except Exception as e:  # the third-party modules are not part of this repository
         return {"unavailable": "transformers/torch import failed: %s" % e}
-    torch.set_num_threads(os.cpu_count() or 1)
+    torch.set_num_threads(host_cores())
     cfg = Qwen3Config(hidden_size=H * D, num_attention_heads=H, num_key_value_heads=HKV,
                       head_dim=D, rope_theta=1e6, max_position_embeddings=1 << 17,
                       num_hidden_layers=1, intermediate_size=64, vocab_size=16)
@@ -886,10 +992,11 @@ def main():
                          "(auto: at N > 1 with the copy-engine gather, where it measured "
                          "5.7 %% faster at 8 GPUs; off at N = 1, where it changes nothing and "
                          "per-kernel times then come from the timed region itself)")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"],
-                    help="per-layer output all-gather at N > 1: 'fused' = peer stores from "
-                         "the attention epilogue (default), 'nccl' = all_gather_into_tensor "
-                         "overlapped on a side stream, 'none' = skipped (diagnostic)")
+    ap.add_argument("--gather", default="copy", choices=["copy", "nccl", "none"],
+                    help="per-layer output all-gather at N > 1: 'copy' = copy-engine copies "
+                         "of this rank's rows into the other ranks' buffers plus flags, on a "
+                         "side stream (default), 'nccl' = all_gather_into_tensor overlapped on "
+                         "a side stream, 'none' = skipped (diagnostic)")
     ap.add_argument("--case", choices=sorted(CASES), default=None,
                     help="run only this single-layer case (for profiler captures)")
     ap.add_argument("--reps", type=int, default=5)

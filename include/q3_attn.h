@@ -468,6 +468,18 @@ bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t layer,
                                     const void *q_host, const void *k_host,
                                     const void *v_host, void *out_host,
                                     char *error, size_t error_len);
+/* The same for head-sharded runs: copies q/k/v in, runs
+ * q3_suffix_attention_layer_gathered (rows into this rank's slot of its own
+ * gathered buffer, copies to the other ranks and flags queued behind them) and
+ * copies this rank's rows [tokens][n_heads][128] back to `out_host`. The
+ * caller alternates two gathered buffers from layer to layer and waits
+ * (q3_attn_wait_gathered) exactly as with the device-pointer call. */
+bool q3_suffix_attention_layer_gathered_host(q3_pack_plan *plan, uint32_t layer,
+                                             const void *q_host, const void *k_host,
+                                             const void *v_host,
+                                             const q3_gather_peers *gather, uint32_t seq,
+                                             void *out_host, char *error,
+                                             size_t error_len);
 
 /* --- diagnostics: the launch schedule (pure host, no CUDA) ---------------- *
  * The tensor-core attention kernel is launched with one CTA per SM; the host

@@ -372,6 +372,14 @@ class PackPlan:
         _call(lib().q3_suffix_attention_layer_gathered, self.h, layer, _ptr(q), _ptr(k),
               _ptr(v), ctypes.byref(peers), seq)
 
+    def attention_layer_gathered_host(self, layer, q, k, v, peers, seq, out):
+        """Host-buffer variant of attention_layer_gathered: q/k/v/out are pinned
+        host torch tensors; `out` receives this rank's rows."""
+        _call(lib().q3_suffix_attention_layer_gathered_host, self.h, layer,
+              ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()),
+              ctypes.c_void_p(v.data_ptr()), ctypes.byref(peers), seq,
+              ctypes.c_void_p(out.data_ptr()))
+
     def attention_layer_host(self, layer, q, k, v, out):
         """q/k/v/out: pinned host torch tensors."""
         _call(lib().q3_suffix_attention_layer_host, self.h, layer,

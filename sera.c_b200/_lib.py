@@ -169,6 +169,8 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     sig("q3_pack_plan_branch_offsets", up, [vp])
     sig("q3_suffix_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)
     sig("q3_suffix_attention_layer_host", b, [vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_suffix_attention_layer_gathered_host", b,
+        [vp, u32, vp, vp, vp, ctypes.POINTER(GatherPeers), u32, vp] + err)
     sig("q3_suffix_attention_layer_gathered", b,
         [vp, u32, vp, vp, vp, ctypes.POINTER(GatherPeers), u32] + err)
     sig("q3_attn_wait_gathered", b, [vp, ctypes.POINTER(GatherPeers), u32] + err)

@@ -602,9 +602,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     for (uint32_t i = 0; i < 64; i++) {
                         if (i == 32) {
                             /* keys 0..63 are ready. The P buffer still feeds the
-                             * previous key tile's PV until pv_done says otherwise. */
+                             * previous key tile's PV until pv_done says otherwise
+                             * (the second half's completion implies the first's:
+                             * one thread issues both, in order). */
                             if (it > 0) {
-                                alive = wait_or_abort(&bar.pv_done[q][0], (it - 1u) & 1u, misc);
+                                alive = wait_or_abort(&bar.pv_done[q][1], (it - 1u) & 1u, misc);
                                 alive = __all_sync(0xffffffffu, alive);
                             }
                             if (alive) {
@@ -633,12 +635,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     l += a0 + a1;
                 }
                 if (!alive) break;
-                if (it > 0) {
-                    alive = wait_or_abort(&bar.pv_done[q][1], (it - 1u) & 1u, misc);
-                    alive = __all_sync(0xffffffffu, alive);
-                    if (!alive) break;
-                }
-                tc_fence_after();
                 tmem_st32(p_addr + 32u, pk + 32);
                 tmem_wait_st();
                 tc_fence_before();

@@ -1132,11 +1132,11 @@ extern "C" bool q3_cuda_qknorm_rope_kvwrite(q3_attn_runtime *rt, uint32_t layer,
 /* host-buffer entry                                                       */
 /* ---------------------------------------------------------------------- */
 
-extern "C" bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t layer,
-                                               const void *q_host,
-                                               const void *k_host,
-                                               const void *v_host, void *out_host,
-                                               char *error, size_t error_len) {
+/* Shared by the two host-buffer entries; gather == NULL: plain layer call. */
+static bool host_layer(q3_pack_plan *plan, uint32_t layer, const void *q_host,
+                       const void *k_host, const void *v_host, void *out_host,
+                       const q3_gather_peers *gather, uint32_t seq, char *error,
+                       size_t error_len) {
     q3_clear_error(error, error_len);
     if (!plan || !q_host || !k_host || !v_host || !out_host)
         return q3_fail(error, error_len,
@@ -1195,16 +1195,52 @@ extern "C" bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t laye
     if (e == cudaSuccess) e = cudaStreamWaitEvent(rt->stream, rt->ev_in[slot], 0);
     if (e != cudaSuccess)
         return q3_fail_cuda(error, error_len, "q3_suffix_attention_layer_host: H2D", e);
-    if (!q3_suffix_attention_layer(plan, layer, dq, dk, dv, dout, error, error_len))
+    const void *result = dout;
+    if (gather) {
+        /* The rows land in this rank's slot of its own gathered buffer, which
+         * the caller alternates between two buffers: the copy-out of the call
+         * two back read the buffer this call overwrites. */
+        if (rt->host_calls >= 3)
+            e = cudaStreamWaitEvent(rt->stream, rt->ev_out[(slot + 1) % 3], 0);
+        if (e != cudaSuccess)
+            return q3_fail_cuda(error, error_len, "q3_suffix_attention_layer_host: order", e);
+        if (!q3_suffix_attention_layer_gathered(plan, layer, dq, dk, dv, gather, seq, error,
+                                                error_len))
+            return false;
+        result = (const uint8_t *)gather->gathered[gather->rank] + ob * gather->rank;
+    } else if (!q3_suffix_attention_layer(plan, layer, dq, dk, dv, dout, error, error_len)) {
         return false;
+    }
     e = cudaEventRecord(rt->ev_compute[slot], rt->stream);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(rt->d2h_stream, rt->ev_compute[slot], 0);
     if (e == cudaSuccess)
-        e = cudaMemcpyAsync(out_host, dout, ob, cudaMemcpyDeviceToHost, rt->d2h_stream);
+        e = cudaMemcpyAsync(out_host, result, ob, cudaMemcpyDeviceToHost, rt->d2h_stream);
     if (e == cudaSuccess) e = cudaEventRecord(rt->ev_out[slot], rt->d2h_stream);
     if (e != cudaSuccess)
         return q3_fail_cuda(error, error_len, "q3_suffix_attention_layer_host: D2H", e);
     return true;
+}
+
+extern "C" bool q3_suffix_attention_layer_host(q3_pack_plan *plan, uint32_t layer,
+                                               const void *q_host,
+                                               const void *k_host,
+                                               const void *v_host, void *out_host,
+                                               char *error, size_t error_len) {
+    return host_layer(plan, layer, q_host, k_host, v_host, out_host, NULL, 0, error,
+                      error_len);
+}
+
+extern "C" bool q3_suffix_attention_layer_gathered_host(
+    q3_pack_plan *plan, uint32_t layer, const void *q_host, const void *k_host,
+    const void *v_host, const q3_gather_peers *gather, uint32_t seq, void *out_host,
+    char *error, size_t error_len) {
+    if (!gather) {
+        q3_clear_error(error, error_len);
+        return q3_fail(error, error_len,
+                       "q3_suffix_attention_layer_gathered_host: invalid argument");
+    }
+    return host_layer(plan, layer, q_host, k_host, v_host, out_host, gather, seq, error,
+                      error_len);
 }
 
 /* ---------------------------------------------------------------------- */

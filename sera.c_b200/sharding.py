@@ -44,13 +44,16 @@ def gathered_to_full(gathered):
 
 
 class PeerGather:
-    """Gathered output buffers in symmetric memory, for the attention kernels
-    that store their rows straight into every rank's buffer.
+    """Gathered output buffers in symmetric memory for the per-layer exchange of
+    q3_suffix_attention_layer_gathered.
 
     Each rank owns `depth` buffers [n, T, H/n, D] and one flag array per
     buffer; `peers(i)` returns the descriptor (peer-mapped base pointers of all
-    ranks) the C ABI takes. No kernel of this repository loads from a peer:
-    ranks only store to peers and read their own memory.
+    ranks) the C ABI takes. The attention kernel writes this rank's slot of its
+    own buffer; copy-engine copies (cudaMemcpyAsync over NVLink, no SM) push
+    that slot into the other ranks' buffers and a one-thread kernel publishes
+    the flags. Nothing loads from a peer: ranks only write to peers and read
+    their own memory.
     """
 
     def __init__(self, tokens, n_heads_local, head_dim, dtype, device, group=None, depth=2):

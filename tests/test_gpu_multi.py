@@ -1,5 +1,6 @@
-"""Two-GPU test of the attention kernels that store their rows into every rank's
-gathered buffer (q3_suffix_attention_layer_gathered): the gathered result must
+"""Two-GPU test of the per-layer output exchange
+(q3_suffix_attention_layer_gathered: attention into this rank's slot, copy-engine
+copies into the other ranks' gathered buffers, flags): the gathered result must
 equal what a single GPU holding all heads produces. Skipped with fewer than two
 GPUs. Ranks are child processes, one per GPU; nothing here waits without bound."""
 import os
@@ -80,6 +81,25 @@ def _worker(rank, world, port, ret):
                 ok = ok and np.array_equal(pg.full(it).float().cpu().numpy(), want)
             dist.barrier()
         graph.close()
+        # host-buffer variant: q/k/v from pinned host memory, this rank's rows back
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+        outs = [torch.zeros(S, qc, D, dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+        for b in pg.bufs:
+            b.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        for it in range(4):                      # three staging slots and two buffers wrap
+            if it >= 2:
+                rt.wait_gathered(pg.peers(it), it - 1)
+            plan.attention_layer_gathered_host(1, hq, hk, hv, pg.peers(it), it + 1, outs[it])
+        rt.wait_gathered(pg.peers(2), 3)
+        rt.wait_gathered(pg.peers(3), 4)
+        rt.gather_advance(4)
+        rt.synchronize()
+        for it in range(4):
+            ok = ok and torch.equal(outs[it], ref_local.cpu())
+        ok = ok and np.array_equal(pg.full(3).float().cpu().numpy(), want)
+        dist.barrier()
     ok = ok and rt.stats().device_status == 0
     ret[rank] = bool(ok)
     for o in (plan, bset, prefix):
