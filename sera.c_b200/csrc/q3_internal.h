@@ -235,6 +235,7 @@ bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer,
 
 bool q3_prepare_attention_kernel(char *error, size_t error_len);
 bool q3_prepare_decode_kernel(char *error, size_t error_len);
+bool q3_prepare_kvwrite_kernel(char *error, size_t error_len);
 
 /* Entry points make the runtime's device current: a host that drives several
  * GPUs from one thread would otherwise launch on whichever device it left. */

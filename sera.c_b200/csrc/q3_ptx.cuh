@@ -90,6 +90,15 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
         "l"(m), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
         : "memory");
 }
+/* Untiled bulk copy global -> shared of this CTA: both addresses 16-byte
+ * aligned, size a multiple of 16 bytes. */
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes,
+                                          uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

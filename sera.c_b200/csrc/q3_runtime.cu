@@ -277,7 +277,8 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
         return NULL;
     }
     if (!q3_prepare_attention_kernel(error, error_len) ||
-        !q3_prepare_decode_kernel(error, error_len)) {
+        !q3_prepare_decode_kernel(error, error_len) ||
+        !q3_prepare_kvwrite_kernel(error, error_len)) {
         q3_attn_destroy(rt);
         return NULL;
     }
