@@ -160,6 +160,7 @@ struct q3_branch_set {
     uint32_t live;
     std::vector<uint8_t> in_use;
     std::vector<uint32_t> pages; /* [max_branches][pages_per_branch] */
+    struct q3_decide_state *decide; /* scratch of q3_decide_run, created on first use */
 };
 
 /* Device-resident descriptors + schedule of one attention launch. */
@@ -176,6 +177,8 @@ struct q3_stage {
     const q3_segment *segments;
     const uint32_t *cta_seg_begin;
     uint32_t tokens, n_shared_pages, shared_len, grid;
+    cudaEvent_t uploaded;  /* recorded after the last upload from `host` */
+    bool has_uploaded;
     /* prefill chunks: which (base, tokens) the staged schedule describes */
     bool chunk_valid;
     uint32_t chunk_base, chunk_tokens;
@@ -214,6 +217,11 @@ bool q3_stage_upload(q3_stage *st, const q3_schedule &sched,
                      const std::vector<uint32_t> &dst_page,
                      const std::vector<uint32_t> &dst_slot,
                      char *error, size_t error_len);
+
+bool q3_pack_plan_build(q3_pack_plan *plan, q3_stage *stage, q3_prefix_kv *prefix,
+                        q3_branch_set *set, const q3_suffix_item *items, uint32_t count,
+                        const char *who, char *error, size_t error_len);
+void q3_decide_state_destroy(q3_branch_set *set);
 
 bool q3_launch_kvwrite(q3_attn_runtime *rt, uint32_t layer, const void *q,
                        const void *k, const void *v, uint32_t tokens,

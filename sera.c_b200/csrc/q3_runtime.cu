@@ -503,6 +503,7 @@ void q3_stage_destroy(q3_stage *st) {
     if (!st) return;
     /* the copy that last used the pinned buffer may still be queued */
     if (st->rt && st->rt->stream) cudaStreamSynchronize(st->rt->stream);
+    if (st->has_uploaded) cudaEventDestroy(st->uploaded);
     if (st->host) cudaFreeHost(st->host);
     if (st->dev) rt_free(st->rt, st->dev);
     delete st;
@@ -546,10 +547,11 @@ bool q3_stage_upload(q3_stage *st, const q3_schedule &s,
             rt_malloc(rt, &st->dev, cap) != cudaSuccess)
             return q3_fail(error, error_len, "stage: allocation failed");
         st->bytes = cap;
-    } else {
+    } else if (st->has_uploaded && cudaEventQuery(st->uploaded) != cudaSuccess) {
         /* the pinned buffer is rewritten below: the previous upload from it
-         * must have been consumed */
-        cudaStreamSynchronize(rt->stream);
+         * must have been consumed (normally long ago: no wait, no sync counted) */
+        cudaEventSynchronize(st->uploaded);
+        rt->n_sync++;
     }
     uint8_t *h = (uint8_t *)st->host;
     const uint8_t *d = (const uint8_t *)st->dev;
@@ -570,6 +572,12 @@ bool q3_stage_upload(q3_stage *st, const q3_schedule &s,
     cudaError_t e = cudaMemcpyAsync(st->dev, st->host, off, cudaMemcpyHostToDevice,
                                     rt->stream);
     if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "stage: upload", e);
+    if (!st->has_uploaded) {
+        if (cudaEventCreateWithFlags(&st->uploaded, cudaEventDisableTiming) != cudaSuccess)
+            return q3_fail(error, error_len, "stage: event creation failed");
+        st->has_uploaded = true;
+    }
+    cudaEventRecord(st->uploaded, rt->stream);
     return true;
 }
 
@@ -788,6 +796,7 @@ extern "C" q3_branch_set *q3_branch_set_create(q3_prefix_kv *prefix,
     set->max_suffix = max_suffix_tokens;
     set->pages_per_branch = (max_suffix_tokens + Q3_PAGE - 1) / Q3_PAGE;
     set->live = 0;
+    set->decide = nullptr;
     set->in_use.assign(max_branches, 0);
     set->pages.resize((size_t)max_branches * set->pages_per_branch);
     if (!q3_pages_alloc(prefix->rt, (uint32_t)set->pages.size(), set->pages.data(),
@@ -832,6 +841,7 @@ extern "C" void q3_branch_release(q3_branch_set *set, int32_t branch) {
 
 extern "C" void q3_branch_set_destroy(q3_branch_set *set) {
     if (!set) return;
+    q3_decide_state_destroy(set);
     q3_pages_free(set->prefix->rt, set->pages.data(), (uint32_t)set->pages.size());
     delete set;
 }
@@ -914,6 +924,56 @@ static bool q3_prefers_lockstep(const q3_attn_runtime *rt, uint32_t shared_len) 
     return kv_bytes > (48ull << 20);
 }
 
+/* Pack `items` and stage descriptors + schedule into `stage` (grow-once).
+ * Shared by q3_pack_plan_create and q3_decide_run, which keeps its stage in
+ * the branch set so that a warm batch allocates nothing. */
+bool q3_pack_plan_build(q3_pack_plan *plan, q3_stage *stage, q3_prefix_kv *prefix,
+                        q3_branch_set *set, const q3_suffix_item *items, uint32_t count,
+                        const char *who, char *error, size_t error_len) {
+    char msg[160];
+    auto fail = [&](const char *what) {
+        snprintf(msg, sizeof(msg), "%s: %s", who, what);
+        return q3_fail(error, error_len, msg);
+    };
+    if (!prefix->sealed) return fail("prefix not sealed");
+    if (set->prefix != prefix) return fail("branch set belongs to another prefix");
+    q3_attn_runtime *rt = prefix->rt;
+    uint64_t total = 0;
+    for (uint32_t b = 0; b < count; b++) total += items[b].token_count;
+    if (count == 0 || total == 0) return fail("bad branch count");
+    if (total > rt->cfg.max_tokens) return fail("packed batch exceeds runtime capacity");
+    if ((uint64_t)prefix->token_count + set->max_suffix > rt->cfg.max_positions)
+        return fail("suffix positions exceed max_positions");
+    plan->prefix = prefix;
+    plan->set = set;
+    plan->branches = count;
+    plan->stage = stage;
+    plan->token_positions.resize(total);
+    plan->token_branch.resize(total);
+    plan->token_local_pos.resize(total);
+    plan->branch_offsets.resize(count + 1);
+    const int64_t packed = q3_pack_suffix_host(
+        items, count, prefix->token_count, set->max_branches, set->max_suffix,
+        plan->token_positions.data(), plan->token_branch.data(),
+        plan->token_local_pos.data(), plan->branch_offsets.data(), error, error_len);
+    if (packed < 0) return false;
+    plan->tokens = (uint32_t)packed;
+    std::vector<uint32_t> dpage(plan->tokens), dslot(plan->tokens);
+    for (uint32_t t = 0; t < plan->tokens; t++) {
+        const uint32_t b = plan->token_branch[t], lp = plan->token_local_pos[t];
+        dpage[t] = set->pages[(size_t)b * set->pages_per_branch + lp / Q3_PAGE];
+        dslot[t] = lp % Q3_PAGE;
+    }
+    q3_schedule s;
+    return q3_build_schedule(s, plan->tokens, rt->cfg.n_kv_heads, prefix->token_count,
+                             prefix->pages, plan->token_branch.data(),
+                             plan->token_local_pos.data(), set->pages,
+                             set->pages_per_branch, (uint32_t)rt->num_sms, rt->part_slots,
+                             q3_prefers_lockstep(rt, prefix->token_count), error,
+                             error_len) &&
+           q3_stage_upload(stage, s, plan->token_positions, dpage, dslot, error, error_len);
+}
+
 extern "C" q3_pack_plan *q3_pack_plan_create(q3_prefix_kv *prefix,
                                              q3_branch_set *set,
                                              const q3_suffix_item *items,
@@ -924,72 +984,16 @@ extern "C" q3_pack_plan *q3_pack_plan_create(q3_prefix_kv *prefix,
         q3_fail(error, error_len, "q3_pack_plan_create: invalid argument");
         return NULL;
     }
-    if (!prefix->sealed) {
-        q3_fail(error, error_len, "q3_pack_plan_create: prefix not sealed");
-        return NULL;
-    }
-    if (set->prefix != prefix) {
-        q3_fail(error, error_len,
-                "q3_pack_plan_create: branch set belongs to another prefix");
-        return NULL;
-    }
-    q3_attn_runtime *rt = prefix->rt;
-    uint64_t total = 0;
-    for (uint32_t b = 0; b < count; b++) total += items[b].token_count;
-    if (count == 0 || total == 0) {
-        q3_fail(error, error_len, "q3_pack_plan_create: bad branch count");
-        return NULL;
-    }
-    if (total > rt->cfg.max_tokens) {
-        q3_fail(error, error_len,
-                "q3_pack_plan_create: packed batch exceeds runtime capacity");
-        return NULL;
-    }
-    if ((uint64_t)prefix->token_count + set->max_suffix > rt->cfg.max_positions) {
-        q3_fail(error, error_len,
-                "q3_pack_plan_create: suffix positions exceed max_positions");
-        return NULL;
-    }
     q3_pack_plan *plan = new (std::nothrow) q3_pack_plan();
-    if (!plan) {
-        q3_fail(error, error_len, "q3_pack_plan_create: allocation failed");
-        return NULL;
-    }
-    plan->prefix = prefix;
-    plan->set = set;
-    plan->branches = count;
-    plan->stage = nullptr;
-    plan->token_positions.resize(total);
-    plan->token_branch.resize(total);
-    plan->token_local_pos.resize(total);
-    plan->branch_offsets.resize(count + 1);
-    const int64_t packed = q3_pack_suffix_host(
-        items, count, prefix->token_count, set->max_branches, set->max_suffix,
-        plan->token_positions.data(), plan->token_branch.data(),
-        plan->token_local_pos.data(), plan->branch_offsets.data(), error, error_len);
-    if (packed < 0) {
+    q3_stage *stage = plan ? q3_stage_create(prefix->rt, error, error_len) : nullptr;
+    if (!plan || !stage) {
+        if (!plan) q3_fail(error, error_len, "q3_pack_plan_create: allocation failed");
         delete plan;
         return NULL;
     }
-    plan->tokens = (uint32_t)packed;
-    std::vector<uint32_t> dpage(plan->tokens), dslot(plan->tokens);
-    for (uint32_t t = 0; t < plan->tokens; t++) {
-        const uint32_t b = plan->token_branch[t], lp = plan->token_local_pos[t];
-        dpage[t] = set->pages[(size_t)b * set->pages_per_branch + lp / Q3_PAGE];
-        dslot[t] = lp % Q3_PAGE;
-    }
-    q3_schedule s;
-    plan->stage = q3_stage_create(rt, error, error_len);
-    if (!plan->stage ||
-        !q3_build_schedule(s, plan->tokens, rt->cfg.n_kv_heads, prefix->token_count,
-                           prefix->pages, plan->token_branch.data(),
-                           plan->token_local_pos.data(), set->pages,
-                           set->pages_per_branch, (uint32_t)rt->num_sms,
-                           rt->part_slots, q3_prefers_lockstep(rt, prefix->token_count),
-                           error, error_len) ||
-        !q3_stage_upload(plan->stage, s, plan->token_positions, dpage, dslot, error,
-                         error_len)) {
-        q3_stage_destroy(plan->stage);
+    if (!q3_pack_plan_build(plan, stage, prefix, set, items, count, "q3_pack_plan_create",
+                            error, error_len)) {
+        q3_stage_destroy(stage);
         delete plan;
         return NULL;
     }
