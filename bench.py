@@ -683,13 +683,85 @@ CASES.update({
 })
 
 
+def case_fp32_surface_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=10):
+    """The reference's own fp32 entry points (rms_norm, rope_positions,
+    attention_segmented; fp32 contiguous slabs, descriptors in host memory as
+    its caller keeps them) served by this library after
+    q3_cuda_attention_native_init: the sequence the reference's
+    run_layer_packed executes, timed as the same-box reference kernels are."""
+    import ctypes
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _gpu_harness as harness
+    L = harness.fp32_surface(pkg.lib_path())
+    lib = pkg.lib()
+    err = ctypes.create_string_buffer(256)
+    f32 = torch.float32
+    S = B * n
+    g = torch.Generator(device=device).manual_seed(0)
+    qs = torch.randn(S, H, D, generator=g, dtype=f32, device=device)
+    ks = torch.randn(S, HKV, D, generator=g, dtype=f32, device=device)
+    pk = torch.randn(1, P, HKV, D, generator=g, dtype=f32, device=device)
+    pv = torch.randn(1, P, HKV, D, generator=g, dtype=f32, device=device)
+    sk = torch.randn(B, 1, n, HKV * D, generator=g, dtype=f32, device=device)
+    sv = torch.randn(B, 1, n, HKV * D, generator=g, dtype=f32, device=device)
+    tb = np.repeat(np.arange(B, dtype=np.uint32), n)
+    tl = np.tile(np.arange(n, dtype=np.uint32), B)
+    pos = torch.from_numpy((tl + P).astype(np.int32)).to(device)
+    ones = torch.ones(D, dtype=f32, device=device)
+    ifr = torch.tensor((1.0 / (1e6 ** (np.arange(D // 2) * 2.0 / D))).astype(np.float32),
+                       device=device)
+    o = torch.zeros_like(qs)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    scale = float(1.0 / np.sqrt(D))
+
+    def ck(ok):
+        if not ok:
+            raise RuntimeError(err.value.decode())
+
+    def run():
+        ck(L.q3_cuda_rms_norm(p(qs), p(ones), S * H, D, 1e-6, p(qs), None, err, 256))
+        ck(L.q3_cuda_rms_norm(p(ks), p(ones), S * HKV, D, 1e-6, p(ks), None, err, 256))
+        ck(L.q3_cuda_rope_positions(p(qs), p(ks), S, H, HKV, D, p(pos), p(ifr), None, err, 256))
+        ck(L.q3_cuda_attention_segmented(p(qs), p(pk), p(pv), P, P, p(sk), p(sv), n, 1, 0,
+                                         ctypes.c_void_p(tb.ctypes.data),
+                                         ctypes.c_void_p(tl.ctypes.data), S, H, HKV, D, scale,
+                                         p(o), None, err, 256))
+
+    pkg._call(lib.q3_cuda_attention_native_init, device.index, S, P + B * 32, H, HKV)
+    try:
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        path = lib.q3_cuda_attention_last_path().decode()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        pkg._call(lib.q3_cuda_attention_native_synchronize, device.index)
+        ms = e0.elapsed_time(e1) / reps
+    finally:
+        lib.q3_cuda_attention_native_shutdown(device.index)
+    pairs = S * P + B * n * (n + 1) // 2
+    return {"ms": ms, "tflops": 4 * D * H * pairs / (ms * 1e-3) / 1e12,
+            "suffix_tokens_per_s": S / (ms * 1e-3), "path": path,
+            "note": "fp32 norm + rope + attention_segmented per call; the attention call "
+                    "converts q and the K/V slabs to f16 pages, builds its schedule on the "
+                    "host and runs the tensor-core kernel"}
+
+
+CASES["fp32_surface_cascade_p8192_b64x24"] = \
+    lambda pkg, torch, dev, reps: case_fp32_surface_cascade(pkg, torch, dev, reps=reps)
+
+
 def run_extras(pkg, torch, device):
     """The other single-GPU configurations of the benchmark definition, one
     layer each: causal prefill (TFLOP/s), 8192-prefix cascade (tokens/s),
     paged decode (GB/s). Device-timed, inputs resident."""
     return {name: CASES[name](pkg, torch, device, 20)
             for name in ("prefill_4096", "cascade_p8192_b64x24", "decode_256seq",
-                         "q4k_qkv_2048")}
+                         "q4k_qkv_2048", "fp32_surface_cascade_p8192_b64x24")}
 
 
 def run_case(args):

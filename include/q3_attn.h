@@ -89,6 +89,29 @@ bool q3_cuda_attention_segmented(const float *q, const float *prefix_k,
                                  uint32_t n_heads, uint32_t n_kv_heads,
                                  uint32_t head_dim, float scale, float *out,
                                  void *stream, char *error, size_t error_len);
+/* The two attention entries above through the tensor-core kernel (not in the
+ * reference). After q3_cuda_attention_native_init(device, max_tokens,
+ * max_kv_tokens, n_heads, n_kv_heads) - the one place this surface allocates:
+ * an f16 page pool for max_kv_tokens keys, a query workspace, schedule staging -
+ * a call with head_dim 128, 8 query heads per KV head, scale = 128^-0.5 and
+ * sizes within those limits converts q and the visible K/V slab rows to f16,
+ * runs attention_tc_kernel and writes fp32 `out`, on the caller's stream and
+ * without synchronising. q3_cuda_attention_segmented additionally needs
+ * token_branch / token_local_pos in memory the HOST can read (pageable, pinned
+ * or managed - where the reference's own caller keeps them), because the launch
+ * schedule is built on the host; with device-only descriptors, or any other
+ * geometry, the exact fp32 kernels run as before. Operands are rounded to f16
+ * on this path (agreement with the fp32 kernels about 1e-3, not 1e-4).
+ * q3_cuda_attention_last_path() names the path of the last call ("tensor-core"
+ * or "simt"); q3_cuda_attention_native_synchronize synchronises the last
+ * caller stream used and reports a bounded device wait that gave up. */
+bool q3_cuda_attention_native_init(int device, uint32_t max_tokens, uint32_t max_kv_tokens,
+                                   uint32_t n_heads, uint32_t n_kv_heads, char *error,
+                                   size_t error_len);
+void q3_cuda_attention_native_shutdown(int device);
+const char *q3_cuda_attention_last_path(void);
+bool q3_cuda_attention_native_synchronize(int device, char *error, size_t error_len);
+
 /* The reference's kv_scatter_kernel is file-static (ref: src/q3_forward.cu:529-550,
  * launched at :1507-1515); exported here so run_layer_packed's scatter step has
  * a symbol to call. Same argument meaning as the kernel. */

@@ -122,6 +122,10 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
          vp] + err)
     sig("q3_cuda_kv_scatter", b, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, vp] + err)
     sig("q3_kv_bytes_for_tokens", sz, [u32, u32, u32, u32])
+    sig("q3_cuda_attention_native_init", b, [ctypes.c_int, u32, u32, u32, u32] + err)
+    sig("q3_cuda_attention_native_shutdown", None, [ctypes.c_int])
+    sig("q3_cuda_attention_last_path", ctypes.c_char_p, [])
+    sig("q3_cuda_attention_native_synchronize", b, [ctypes.c_int] + err)
     # ---- part 2: native paged path
     sig("q3_attn_create", vp, [ctypes.POINTER(AttnConfig)] + err)
     sig("q3_attn_destroy", None, [vp])

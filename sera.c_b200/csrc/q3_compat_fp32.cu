@@ -246,6 +246,13 @@ extern "C" bool q3_cuda_attention(const float *q, const float *k, const float *v
         v_src = kv->v + (size_t)layer * per_layer;
         kv_length = kv->length + tokens;
     }
+    {
+        bool ok = false;
+        if (q3_fp32_native_attention(q, k_src, v_src, tokens, n_heads, n_kv_heads, head_dim,
+                                     position_base, kv_length, scale, out, stream, &ok, error,
+                                     error_len))
+            return ok;
+    }
     dim3 grid(tokens, n_heads);
     attention_fp32_kernel<<<grid, 32, 0, (cudaStream_t)stream>>>(
         q, k_src, v_src, out, tokens, n_heads, n_kv_heads, head_dim, position_base,
@@ -268,6 +275,32 @@ extern "C" bool q3_cuda_attention_segmented(
         n_heads % n_kv_heads != 0 || prefix_len > prefix_capacity ||
         suffix_num_layers == 0)
         return q3_fail(error, error_len, "q3_cuda_attention_segmented: invalid argument");
+    if (suffix_layer < suffix_num_layers) {
+        bool ok = false;
+        /* the prefix slabs hold every layer: [layer][prefix_capacity][row] */
+        const size_t pbase = (size_t)suffix_layer * prefix_capacity * n_kv_heads * head_dim;
+        if (q3_fp32_native_segmented(q, prefix_k + pbase, prefix_v + pbase, prefix_len, suffix_k, suffix_v,
+                                     suffix_capacity, suffix_num_layers, suffix_layer,
+                                     token_branch, token_local_pos, tokens, n_heads,
+                                     n_kv_heads, head_dim, scale, out, stream, &ok, error,
+                                     error_len))
+            return ok;
+    }
+    {
+        /* the fp32 kernel dereferences the descriptors on the device: pageable
+         * host memory would fault there (the reference hands its kernels such
+         * memory, which only works on unified-memory parts) */
+        cudaPointerAttributes a, b;
+        const bool known = cudaPointerGetAttributes(&a, token_branch) == cudaSuccess &&
+                           cudaPointerGetAttributes(&b, token_local_pos) == cudaSuccess;
+        if (!known) cudaGetLastError();
+        if (known && (a.type == cudaMemoryTypeUnregistered || b.type == cudaMemoryTypeUnregistered))
+            return q3_fail(error, error_len,
+                           "q3_cuda_attention_segmented: token_branch / token_local_pos are in "
+                           "pageable host memory, which this device cannot read: pass device "
+                           "copies, or enable the tensor-core path "
+                           "(q3_cuda_attention_native_init), which reads them on the host");
+    }
     dim3 grid(tokens, n_heads);
     attention_segmented_fp32_kernel<<<grid, 32, 0, (cudaStream_t)stream>>>(
         q, out, tokens, n_heads, n_kv_heads, head_dim, scale, prefix_k, prefix_v,

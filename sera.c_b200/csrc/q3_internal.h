@@ -222,6 +222,21 @@ bool q3_pack_plan_build(q3_pack_plan *plan, q3_stage *stage, q3_prefix_kv *prefi
                         q3_branch_set *set, const q3_suffix_item *items, uint32_t count,
                         const char *who, char *error, size_t error_len);
 void q3_decide_state_destroy(q3_branch_set *set);
+/* fp32 surface through the tensor-core kernel (q3_fp32_native.cu): return true
+ * when the call was taken (*ok = its outcome), false when it does not apply */
+bool q3_fp32_native_attention(const float *q, const float *k_src, const float *v_src,
+                              uint32_t tokens, uint32_t n_heads, uint32_t n_kv_heads,
+                              uint32_t head_dim, uint32_t position_base, uint32_t kv_length,
+                              float scale, float *out, void *stream, bool *ok, char *error,
+                              size_t error_len);
+bool q3_fp32_native_segmented(const float *q, const float *prefix_k, const float *prefix_v,
+                              uint32_t prefix_len, const float *suffix_k,
+                              const float *suffix_v, uint32_t suffix_capacity,
+                              uint32_t suffix_num_layers, uint32_t suffix_layer,
+                              const uint32_t *token_branch, const uint32_t *token_local_pos,
+                              uint32_t tokens, uint32_t n_heads, uint32_t n_kv_heads,
+                              uint32_t head_dim, float scale, float *out, void *stream,
+                              bool *ok, char *error, size_t error_len);
 
 bool q3_launch_kvwrite(q3_attn_runtime *rt, uint32_t layer, const void *q,
                        const void *k, const void *v, uint32_t tokens,

@@ -135,7 +135,7 @@ def fp32_surface(path):
     return L
 
 
-def run_case_fp32_surface(L, case, inv_freq):
+def run_case_fp32_surface(L, case, inv_freq, host_descriptors=False):
     """Drive the fp32 primitive surface (the reference's, or this library's
     part 1 - same symbols) in the reference's sequencing and slab layout
     (src/q3_forward.cu:1244-1286 and :1489-1526). L is a ctypes library."""
@@ -183,8 +183,15 @@ def run_case_fp32_surface(L, case, inv_freq):
         sk[tbl, layer, tll] = ks.reshape(S, row)
         sv[tbl, layer, tll] = vs.reshape(S, row)
         torch.cuda.synchronize()
+        if host_descriptors:
+            # where the reference's own caller keeps them (src/q3_decide.cu:420-464)
+            hb = np.ascontiguousarray(case.token_branch, np.uint32)
+            hl = np.ascontiguousarray(case.token_local_pos, np.uint32)
+            ptb, ptl = ctypes.c_void_p(hb.ctypes.data), ctypes.c_void_p(hl.ctypes.data)
+        else:
+            ptb, ptl = p(tb), p(tl)
         ck(L.q3_cuda_attention_segmented(p(qs), p(pk), p(pv), P, pcap, p(sk), p(sv), cap,
-                                         Lyr, layer, p(tb), p(tl), S, H, Hkv, D,
+                                         Lyr, layer, ptb, ptl, S, H, Hkv, D,
                                          float(case.scale), p(out[P:]), None, err, 256),
            "segmented")
     torch.cuda.synchronize()

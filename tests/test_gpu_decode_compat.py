@@ -145,6 +145,42 @@ def test_fp32_surface_matches_oracle_and_reference(pkg, name):
     assert np.abs(theirs["out"] - mine["out"]).max() < 5e-4
 
 
+@pytest.mark.parametrize("name", ["ragged", "prefill_only", "config1"])
+def test_fp32_surface_through_the_tensor_core_kernel(pkg, name):
+    """The same fp32 symbols after q3_cuda_attention_native_init: slabs and
+    queries are converted to f16 and attention_tc_kernel runs (tolerance 2e-3:
+    f16 operands); without host-readable descriptors, or after shutdown, the
+    exact fp32 kernels answer."""
+    case = _cases.make_case(name)
+    ifreq = oracle.inv_freq(case.theta, case.D)
+    ref = oracle.run_case(case)
+    L = pkg.lib()
+    surf = harness.fp32_surface(pkg.lib_path())
+    pkg._call(L.q3_cuda_attention_native_init, 0, case.T, case.T + 64, case.H, case.Hkv)
+    try:
+        with pytest.raises(pkg.Q3Error, match="already initialised"):
+            pkg._call(L.q3_cuda_attention_native_init, 0, 8, 8, case.H, case.Hkv)
+        mine = harness.run_case_fp32_surface(surf, case, ifreq, host_descriptors=True)
+        assert L.q3_cuda_attention_last_path() == b"tensor-core"
+        pkg._call(L.q3_cuda_attention_native_synchronize, 0)
+        err = np.abs(mine["out"] - ref["out"]).max()
+        print("%s through the tensor-core kernel: max abs err %.3e" % (name, err))
+        assert err <= ATOL
+        if case.S:
+            # device-only descriptors: the host cannot build a schedule from them
+            harness.run_case_fp32_surface(surf, case, ifreq, host_descriptors=False)
+            assert L.q3_cuda_attention_last_path() == b"simt"
+    finally:
+        L.q3_cuda_attention_native_shutdown(0)
+    exact = harness.run_case_fp32_surface(surf, case, ifreq, host_descriptors=False)
+    assert L.q3_cuda_attention_last_path() == b"simt"
+    assert np.abs(exact["out"] - ref["out"]).max() < 1e-4
+    if case.S:
+        # pageable host descriptors without the tensor-core path: refused, not dereferenced
+        with pytest.raises(RuntimeError, match="pageable host memory"):
+            harness.run_case_fp32_surface(surf, case, ifreq, host_descriptors=True)
+
+
 def test_fp32_kv_cache_split_equals_contiguous(pkg):
     """tests/test_q3_forward.cu:388-483 on the fp32 surface: T=8 one-shot vs
     prefix 4 + suffix 4 through q3_kv_cache, last token's rows."""
