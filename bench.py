@@ -948,9 +948,10 @@ def python_path_baseline():
     """The reference's Python path for this arithmetic: the HuggingFace Qwen3
     functions its oracle scripts execute (RMSNorm, rotary embedding,
     apply_rotary_pos_emb, repeat_kv) plus torch SDPA, on CPU in fp32 with all
-    host threads (ref: tools/qwen3_q4_oracle.py:88-92,151-154). Prefill at 4096
-    tokens and the 8192-token-prefix cascade case, one repeat each after a
-    warm-up on a tenth of the size."""
+    host threads (ref: tools/qwen3_q4_oracle.py:88-92,151-154). Configuration 1
+    in full, prefill at 4096 tokens, the 8192-token-prefix cascade case, a
+    32-sequence subset of the decode configuration and one layer of the stack
+    with a reduced prefix; one repeat each after a small warm-up."""
     try:
         import torch
         from transformers.models.qwen3 import modeling_qwen3 as m
@@ -993,7 +994,30 @@ def python_path_baseline():
                 torch.nn.functional.scaled_dot_product_attention(qs, kk, vv, attn_mask=mask)
         return time.perf_counter() - t0
 
+    def decode(ctx_lens):
+        """One query token per sequence over its own context (paged decode's arithmetic)."""
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            for c in ctx_lens:
+                c = int(c)
+                q = torch.randn(1, 1, H, D, generator=gen)
+                k = torch.randn(1, c, HKV, D, generator=gen)
+                v = torch.randn(1, c, HKV, D, generator=gen)
+                qs = qn(q).transpose(1, 2)
+                ks = kn(k).transpose(1, 2)
+                cos, sin = rot(v, torch.arange(c)[None])
+                qs, _ = m.apply_rotary_pos_emb(qs, qs, cos[:, -1:], sin[:, -1:])
+                ks, _ = m.apply_rotary_pos_emb(ks, ks, cos, sin)
+                kk, vv = m.repeat_kv(ks, H // HKV), m.repeat_kv(v.transpose(1, 2), H // HKV)
+                torch.nn.functional.scaled_dot_product_attention(qs, kk, vv)
+        return time.perf_counter() - t0
+
     res = {"cores": torch.get_num_threads()}
+    # configuration 1 in full: 256-token prefix + 3 branches x 8 tokens
+    run(64, 2, 4)
+    t = run(256, 3, 8)
+    res["config1_p256_b3x8"] = {"ms": t * 1e3, "suffix_tokens_per_s": 24 / t,
+                                "note": "prefix rows are computed too (280 query rows)"}
     run(400, 0, 0)
     t = run(4096, 0, 0)
     res["prefill_4096"] = {"ms": t * 1e3, "tokens_per_s": 4096 / t,
@@ -1004,6 +1028,23 @@ def python_path_baseline():
         "ms": t * 1e3, "suffix_tokens_per_s": 1536 / t,
         "tflops": 4 * D * H * (1536 * 8192 + 64 * 300) / t / 1e12,
         "note": "includes norm + rope of the 8192 prefix keys, which the GPU path keeps resident"}
+    # configuration 4 on a 32-sequence subset (the first 32 of the seeded context lengths;
+    # random data generation is inside the time, about a tenth of it)
+    ctx = np.random.default_rng(1).integers(1024, 16385, 256)[:32]
+    decode(ctx[:2])
+    t = decode(ctx)
+    res["decode_32_of_256_sequences"] = {
+        "ms": t * 1e3, "seq_tokens_per_s": 32 / t, "sum_ctx": int(ctx.sum()),
+        "note": "32 of the 256 sequences, norm + rope of every context key included "
+                "(the GPU path keeps them resident)"}
+    # configuration 5: one layer, prefix reduced from 32768 to 4096 tokens, all 128 x 16
+    # suffix tokens; scaled by 8 (attention work is linear in the prefix) and by 64 layers
+    t = run(4096, BRANCHES, SUFFIX)
+    res["stack_layer_p4096_of_32768_b128x16"] = {
+        "ms": t * 1e3, "suffix_tokens_per_s": TOKENS / t,
+        "stack64_tokens_per_s_extrapolated": TOKENS / (t * 8 * L),
+        "note": "one of 64 layers, prefix 4096 of 32768 tokens; extrapolation = x8 for the "
+                "prefix, x64 for the layers"}
     return res
 
 

@@ -19,7 +19,7 @@ LIB = os.path.join(PKG, "libq3attn.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 SOURCES = ["q3_runtime.cu", "q3_kvwrite.cu", "q3_attn_tc.cu", "q3_attn_decode.cu",
-           "q3_compat_fp32.cu", "q3_fp32_native.cu", "q3_decide.cu", "q3_q4k_linear.cu", "q3_q4k_small.cu", "q3_q4k_mmvq.cu", "q3_lmhead.cu", "q3_sched.cpp", "q3_diag.cpp", "q3_prefix_cache.cpp"]
+           "q3_compat_fp32.cu", "q3_fp32_native.cu", "q3_decide.cu", "q3_q4k_linear.cu", "q3_q4k_small.cu", "q3_q4k_mmvq.cu", "q3_q4k_generic.cu", "q3_lmhead.cu", "q3_sched.cpp", "q3_diag.cpp", "q3_prefix_cache.cpp"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
          "-std=c++17", "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"),
          "-I" + CSRC]

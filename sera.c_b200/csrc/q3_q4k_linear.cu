@@ -52,6 +52,9 @@ bool q3_launch_q4k_small(const void *weight, const void *x_f16, uint32_t M, uint
 /* q3_q4k_mmvq.cu */
 #define Q3_MMVQ_MAX_BATCH 8u
 size_t q3_q4k_mmvq_workspace_bytes(size_t tokens, size_t k);
+bool q3_launch_q4k_generic(uint32_t qtype, const void *weight, const void *x_f16, uint32_t M,
+                           uint32_t N, uint32_t K, void *out, uint32_t out_type,
+                           cudaStream_t stream, char *error, size_t error_len);
 bool q3_launch_q4k_mmvq(const void *weight, const float *x, uint32_t M, uint32_t N, uint32_t K,
                         float *out, void *workspace, cudaStream_t stream, char *error,
                         size_t error_len);
@@ -581,10 +584,13 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
                    size_t tokens, void *out, uint32_t out_type, cudaStream_t stream,
                    char *error, size_t error_len) {
     const uint32_t M = (uint32_t)tokens, N = (uint32_t)geo->N, K = (uint32_t)geo->K;
-    if (geo->qtype == Q3_QUANT_Q6_K)
-        return q3_fail(error, error_len,
-                       "q3_q4_linear: a Q6_K weight must first be re-laid out with "
-                       "q3_cuda_q4k_linear_pack (210-byte blocks cannot be fetched by TMA)");
+    /* GGUF-order Q6_K (210-byte blocks cannot be fetched by TMA) and feature
+     * counts off the 128 grid: the plain kernel, so that no caller of the
+     * reference's entry point is refused where the reference runs. Re-laying a
+     * Q6_K weight out once with q3_cuda_q4k_linear_pack gives the tile kernel. */
+    if (geo->qtype == Q3_QUANT_Q6_K || (geo->qtype == Q3_QUANT_Q4_K && (N % 128u) != 0))
+        return q3_launch_q4k_generic(geo->qtype, weight, x_f16, M, N, K, out, out_type, stream,
+                                     error, error_len);
     if (geo->qtype != Q3_QUANT_Q4_K && geo->qtype != Q3_QUANT_Q4_K_TILED &&
         geo->qtype != Q3_QUANT_Q6_K_TILED)
         return q3_fail(error, error_len, "q3_q4_linear: weight is neither Q4_K nor Q6_K");

@@ -170,6 +170,39 @@ def test_long_suffixes_many_tiles(pkg):
     assert np.array_equal(_candidate_argmax(got, case), _candidate_argmax(ref, case))
 
 
+def test_guard_rows_around_outputs_and_pool(pkg):
+    """Stand-in for a memory checker: the attention output sits between guard
+    rows filled with a sentinel, and every page of the pool that the batch does
+    not own must stay zero - in the layer that ran and in the one that did not.
+    The shape cuts every item into pieces (2 KV heads x few key tiles on all
+    CTAs), so the partial-combination path writes the rows."""
+    case = harness.rounded_case(_cases.Case("guard", 700, [130, 9, 40], n_heads=16,
+                                            n_kv_heads=2, seed=13))
+    got, rt, prefix, bset, plan = harness.run_case_native(pkg, case, out_fp32=True,
+                                                          return_runtime=True)
+    P, S, H, D = case.P, case.S, case.H, case.D
+    GUARD, SENT = 64, 12345.0
+    buf = torch.full((GUARD + S + GUARD, H, D), SENT, dtype=torch.float32, device="cuda")
+    q, k, v = (harness.dev(a[P:], torch.bfloat16) for a in (case.q, case.k, case.v))
+    torch.cuda.synchronize()
+    plan.attention_layer(1, q, k, v, buf[GUARD:GUARD + S])
+    rt.synchronize()
+    assert rt.stats().device_status == 0
+    assert bool((buf[:GUARD] == SENT).all()) and bool((buf[GUARD + S:] == SENT).all())
+    assert np.array_equal(buf[GUARD:GUARD + S].cpu().numpy(), got[P:])
+    kp, vp = rt.pool()
+    owned = set(prefix.page_table().tolist()) | set(bset.page_table().reshape(-1).tolist())
+    free = torch.tensor([i for i in range(rt.cfg.num_pages) if i not in owned],
+                        dtype=torch.long, device="cuda")
+    assert len(free) >= 7
+    for pool in (kp, vp):
+        assert float(pool[1][:, free].abs().max()) == 0.0
+        assert float(pool[0].abs().max()) == 0.0
+    for o in (plan, bset, prefix):
+        o.close()
+    rt.close()
+
+
 def test_warm_path_counters(pkg):
     """Zero allocations and zero host syncs across repeated layers of a batch
     (the reference's gate, tests/test_q3_decide.cu:632-821), and repeatability."""

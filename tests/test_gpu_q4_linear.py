@@ -86,17 +86,18 @@ def test_tiled_weight_layout_is_bit_identical(lin, M, N, K):
 def test_q6k_weight_through_the_tiled_layout(lin, M, N, K):
     """Q6_K (attn_v / ffn_down / output tensors of a Q4_K_M file): packed once
     into 224-byte slots, then the same kernel with the Q6_K conversion. Parity
-    bars as for Q4_K; the GGUF order itself is refused."""
+    bars as for Q4_K. The GGUF order itself runs through the plain kernel
+    (fp32 dequantisation: exact bars)."""
     q4, L = lin
-    from sera_c_b200 import Q3Error
     rng = np.random.default_rng(M + N + K)
     w = qo.q6k_random_blocks(rng, N * (K // 256)).reshape(N, -1)
     x = rng.standard_normal((M, K)).astype(np.float32)
     geo = q4.bind_geometry(K, N, qtype=q4.Q6_K)
     wd = torch.from_numpy(w).cuda()
     xd = torch.from_numpy(x).cuda().half()
-    with pytest.raises(Q3Error, match="re-laid out"):
-        L.linear_f16(geo, wd, xd)
+    plain = L.linear_f16(geo, wd, xd, out_dtype=torch.float32).cpu().numpy()
+    pm = qo.linear_error_metrics(plain, qo.quant_linear(w, 14, xd.float().cpu().numpy()))
+    assert pm["rel_l2"] < 1e-5 and pm["cos"] > 0.999999, pm
     tiled, tgeo = L.pack(geo, wd)
     assert tgeo.qtype == (14 | (1 << 16)) and tiled.numel() == N * (K // 256) * 224
     slots = tiled.cpu().numpy().reshape(N // 128, K // 256, 128, 224)
@@ -207,16 +208,37 @@ def test_fp32_surface_like_the_reference_test(lin, M):
     assert L.status() == 0
 
 
+@pytest.mark.parametrize("qtype", [12, 14])
+@pytest.mark.parametrize("M,N,K", [(1, 200, 512), (8, 72, 256), (19, 1000, 1024)])
+def test_gguf_order_any_feature_count(lin, qtype, M, N, K):
+    """What the reference's entry point accepts and the tile kernels do not:
+    Q6_K in GGUF order and feature counts off the 128 grid (ref:
+    src/q3_q4_linear.cu:149-228), through both the f16 and the fp32 entry."""
+    q4, L = lin
+    rng = np.random.default_rng(qtype + M + N + K)
+    if qtype == 12:
+        w = qo.q4k_weight(rng, N, K)
+    else:
+        w = qo.q6k_random_blocks(rng, N * (K // 256)).reshape(N, -1)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    geo = q4.bind_geometry(K, N, qtype=qtype)
+    wd = torch.from_numpy(w).cuda()
+    xh = torch.from_numpy(x).cuda().half()
+    got = L.linear_f16(geo, wd, xh, out_dtype=torch.float32).cpu().numpy()
+    m = qo.linear_error_metrics(got, qo.quant_linear(w, qtype, xh.float().cpu().numpy()))
+    assert m["rel_l2"] < 1e-5 and m["cos"] > 0.999999, m
+    got32 = L.linear_f32(geo, wd, torch.from_numpy(x).cuda()).cpu().numpy()
+    m32 = qo.linear_error_metrics(got32, qo.quant_linear(w, qtype, x))
+    assert m32["rel_l2"] < 1e-3 and m32["cos"] > 0.99999, m32     # activations pass through f16
+    assert L.status() == 0
+
+
 def test_error_paths(lin):
     q4, L = lin
     from sera_c_b200 import Q3Error
     geo = q4.bind_geometry(512, 256)
     w = torch.zeros(256 * 2 * 144, dtype=torch.uint8, device="cuda")
     x = torch.zeros(8, 512, dtype=torch.float16, device="cuda")
-    with pytest.raises(Q3Error, match="Q6_K weight must first be re-laid out"):
-        L.linear_f16(q4.bind_geometry(512, 256, qtype=q4.Q6_K), w, x)
-    with pytest.raises(Q3Error, match="N of 128"):
-        L.linear_f16(q4.bind_geometry(512, 200), w, x)
     with pytest.raises(Q3Error, match="workspace"):
         big = torch.zeros(5000, 8192, dtype=torch.float32, device="cuda")
         L.linear_f32(q4.bind_geometry(8192, 256), w, big)
