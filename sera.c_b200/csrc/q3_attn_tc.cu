@@ -219,6 +219,16 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity,
     atomicExch(&misc->abort_flag, 1u);
     return false;
 }
+/* For the waits of the softmax threads, which are normally satisfied long
+ * before they are reached: a few non-blocking tests first. */
+__device__ __forceinline__ bool quick_wait_or_abort(uint64_t *bar, uint32_t parity,
+                                                    Misc *misc) {
+#ifndef Q3_NO_QUICK_WAIT
+    for (uint32_t i = 0; i < 8; i++)
+        if (mbar_test_wait(bar, parity)) return true;
+#endif
+    return wait_or_abort(bar, parity, misc);
+}
 /* Abort path only: give a load that is still in flight time to land. */
 __device__ __forceinline__ void drain_wait(uint64_t *bar, uint32_t parity) {
     for (uint32_t i = 0; i < kDrainPolls; i++)
@@ -522,7 +532,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             float m_ref = -INFINITY, l = 0.f;
 
             for (uint32_t j = 0; j < n && alive; j++, it++) {
-                alive = wait_or_abort(&bar.s_full[q], it & 1u, misc);
+                alive = quick_wait_or_abort(&bar.s_full[q], it & 1u, misc);
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 tc_fence_after();
@@ -606,7 +616,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                              * (the second half's completion implies the first's:
                              * one thread issues both, in order). */
                             if (it > 0) {
-                                alive = wait_or_abort(&bar.pv_done[q][1], (it - 1u) & 1u, misc);
+                                alive = quick_wait_or_abort(&bar.pv_done[q][1], (it - 1u) & 1u, misc);
                                 alive = __all_sync(0xffffffffu, alive);
                             }
                             if (alive) {

@@ -57,6 +57,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+/* Non-blocking test: returns at once, where try_wait suspends the thread for a
+ * hardware-defined slice even when the phase has long completed. */
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 /* Bounded wait. try_wait itself blocks for a hardware-defined slice, so the
  * poll count below corresponds to a wall time far beyond any legitimate wait
  * of these kernels (seconds), yet finite. */
