@@ -54,10 +54,10 @@ PAIRS_PER_HEAD = TOKENS * PREFIX + BRANCHES * (SUFFIX * (SUFFIX + 1) // 2)
 FLOPS_PER_LAYER = 4 * D * H * PAIRS_PER_HEAD
 FLOPS_PER_STEP = FLOPS_PER_LAYER * L
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at N = 1, from an
-# ncu capture of `--case stack_layer_p32768_b128x16` (205.8 MB read + 49.9 MB written;
+# ncu capture of `--case stack_layer_p32768_b128x16` (207.4 MB read + 54.0 MB written;
 # algorithmic bytes 218 MB). A constant, not re-measured per run; at N > 1 the per-rank
 # share (1/N of the KV heads) is reported and marked as scaled.
-ATTENTION_DRAM_BYTES_PER_LAUNCH = 255.6e6
+ATTENTION_DRAM_BYTES_PER_LAUNCH = 261.3e6
 
 
 def measured_peaks():
