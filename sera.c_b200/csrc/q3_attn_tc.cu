@@ -670,9 +670,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     if (valid) store_row_chunk(p, orow + ch * 32, v);
                 }
             } else {
-                /* piece of a cut item: publish the un-normalised partial ... */
+                /* piece of a cut item: publish the un-normalised partial ...
+                 * Layout of a piece's O: [M tile][row quarter][32 chunks of 4
+                 * columns][32 lanes] x 16 bytes, so that a warp's store (and the
+                 * combining warp's load) of one chunk is 512 contiguous bytes. */
                 const size_t prow = (size_t)seg.partial_slot * 256 + q * 128 + row;
-                float *dst = p.part_o + prow * Q3_D;
+                uint4 *dst = reinterpret_cast<uint4 *>(p.part_o) +
+                             ((((size_t)seg.partial_slot * 2 + q) * 4 + (warp & 3u)) << 10) + lane;
 #pragma unroll
                 for (uint32_t ch = 0; ch < 4; ch++) {
                     uint32_t o[32];
@@ -680,7 +684,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     tmem_wait_ld();
 #pragma unroll
                     for (uint32_t i = 0; i < 8; i++)
-                        *reinterpret_cast<uint4 *>(dst + ch * 32 + i * 4) =
+                        dst[(ch * 8 + i) * 32] =
                             make_uint4(o[i * 4], o[i * 4 + 1], o[i * 4 + 2], o[i * 4 + 3]);
                 }
                 p.part_ml[prow] =
@@ -724,39 +728,52 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                         }
                     }
                     const float inv = 1.0f / den;
+                    const float w_self = w_own * inv;
+                    const float4 *piece0 =
+                        reinterpret_cast<const float4 *>(p.part_o) +
+                        ((((size_t)seg.slot_begin * 2 + q) * 4 + (warp & 3u)) << 10) + lane;
+                    /* 64 columns per pass: a pass costs one L2 round trip per other
+                     * piece (16 loads of 16 bytes in flight per thread), so the
+                     * whole combination is 2 x (pieces - 1) round trips. Pieces
+                     * are summed in slot order whichever came last: the result is
+                     * bit-identical from run to run. */
 #pragma unroll 1
-                    for (uint32_t ch = 0; ch < 4; ch++) {
-                        uint32_t o[32];
-                        tmem_ld32(o_addr + ch * 32u, o);
-                        tmem_wait_ld();
-                        float v[32];
+                    for (uint32_t hf = 0; hf < 2; hf++) {
+                        float v[64];
 #pragma unroll
-                        for (uint32_t i = 0; i < 32; i++) v[i] = 0.f;
+                        for (uint32_t i = 0; i < 64; i++) v[i] = 0.f;
+#pragma unroll 1
                         for (uint32_t sidx = 0; sidx < seg.slot_count; sidx++) {
                             if (sidx == own) {
-                                const float wgt = w_own * inv;
 #pragma unroll
-                                for (uint32_t i = 0; i < 32; i++)
-                                    v[i] += wgt * __uint_as_float(o[i]);
+                                for (uint32_t c2 = 0; c2 < 2; c2++) {
+                                    uint32_t o[32];
+                                    tmem_ld32(o_addr + hf * 64u + c2 * 32u, o);
+                                    tmem_wait_ld();
+#pragma unroll
+                                    for (uint32_t i = 0; i < 32; i++)
+                                        v[c2 * 32 + i] += w_self * __uint_as_float(o[i]);
+                                }
                                 continue;
                             }
-                            const size_t r2 = base + (size_t)sidx * 256;
-                            const float mx2 = __ldcg(&p.part_ml[r2]).x;
+                            const float4 *src = piece0 + ((size_t)sidx << 13) + hf * 512;
+                            float4 f[16];
+#pragma unroll
+                            for (uint32_t i = 0; i < 16; i++) f[i] = __ldcg(src + i * 32);
+                            const float mx2 = __ldcg(&p.part_ml[base + (size_t)sidx * 256]).x;
                             const float wgt = mx2 == -INFINITY ? 0.f : exp2f(mx2 - M) * inv;
-                            const float4 *src = reinterpret_cast<const float4 *>(
-                                p.part_o + r2 * Q3_D + ch * 32);
-                            float4 f[8];
 #pragma unroll
-                            for (uint32_t i = 0; i < 8; i++) f[i] = __ldcg(src + i);
-#pragma unroll
-                            for (uint32_t i = 0; i < 8; i++) {
+                            for (uint32_t i = 0; i < 16; i++) {
                                 v[i * 4] += wgt * f[i].x;
                                 v[i * 4 + 1] += wgt * f[i].y;
                                 v[i * 4 + 2] += wgt * f[i].z;
                                 v[i * 4 + 3] += wgt * f[i].w;
                             }
                         }
-                        if (valid) store_row_chunk(p, orow + ch * 32, v);
+                        if (valid) {
+                            store_row_chunk(p, orow + hf * 64, v);
+                            store_row_chunk(p, orow + hf * 64 + 32, v + 32);
+                        }
                     }
                 }
             }
