@@ -259,7 +259,9 @@ __device__ __forceinline__ void store_row_chunk(const AttnParams &p, size_t off,
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const AttnParams p) {
+                    const __grid_constant__ CUtensorMap v_map,
+                    const __grid_constant__ CUtensorMap k_map_tile,
+                    const __grid_constant__ CUtensorMap v_map_tile, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Misc *misc = reinterpret_cast<Misc *>(smem + kSmemMisc);
@@ -306,6 +308,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             prefetch_tmap(&q_map);
             prefetch_tmap(&k_map);
             prefetch_tmap(&v_map);
+            prefetch_tmap(&k_map_tile);
+            prefetch_tmap(&v_map_tile);
         }
         uint32_t it = 0;          /* K tiles armed so far */
         uint32_t v_armed = 0;     /* V tiles armed so far */
@@ -339,10 +343,78 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                     (int32_t)(seg.tok0 + q * 16), &bar.q_full);
             }
             q_armed++;
-            for (uint32_t tile = seg.tile_begin; tile < seg.tile_end; tile++) {
+            /* Arm the K and V loads of one key tile: lanes 0..7 fetch one page
+             * each (two 64-column boxes) from pool row `row`; when the eight
+             * pages follow one another in the pool (`run`), lane 0 fetches
+             * them as two boxes of 128 rows. A copy costs the issuing warp
+             * about 60 clocks whatever its size, one lane after the other:
+             * 32 page copies per key tile are 2 k clocks of this warp, more
+             * than the tensor work of the tile. */
+            auto arm_tile = [&](int32_t row, bool run) {
                 const uint32_t stage = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
-                /* lanes 0..7 resolve one page slot each */
+                if (lane == 0) mbar_arrive_expect_tx(&bar.k_full[stage], kTileBytes);
+                __syncwarp();
+                if (run) {
+                    if (lane == 0) {
+                        uint8_t *dst = smem + kSmemK + stage * kTileBytes;
+                        tma_load_2d(dst, &k_map_tile, 0, row, &bar.k_full[stage]);
+                        tma_load_2d(dst + kHalfBytes, &k_map_tile, 64, row, &bar.k_full[stage]);
+                    }
+                } else if (lane < 8) {
+                    uint8_t *dst = smem + kSmemK + stage * kTileBytes + lane * kPageHalfBytes;
+                    tma_load_2d(dst, &k_map, 0, row, &bar.k_full[stage]);
+                    tma_load_2d(dst + kHalfBytes, &k_map, 64, row, &bar.k_full[stage]);
+                }
+                it++;
+                alive = wait_or_abort(&bar.v_empty[stage], ph ^ 1u, misc);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) return;
+                if (lane == 0) mbar_arrive_expect_tx(&bar.v_full[stage], kTileBytes);
+                __syncwarp();
+                if (run) {
+                    if (lane == 0) {
+                        uint8_t *dst = smem + kSmemV + stage * kTileBytes;
+                        tma_load_2d(dst, &v_map_tile, 0, row, &bar.v_full[stage]);
+                        tma_load_2d(dst + kHalfBytes, &v_map_tile, 64, row, &bar.v_full[stage]);
+                    }
+                } else if (lane < 8) {
+                    uint8_t *dst = smem + kSmemV + stage * kTileBytes + lane * kPageHalfBytes;
+                    tma_load_2d(dst, &v_map, 0, row, &bar.v_full[stage]);
+                    tma_load_2d(dst + kHalfBytes, &v_map, 64, row, &bar.v_full[stage]);
+                }
+                v_armed++;
+            };
+            const uint32_t row_base = p.pool_row_base + seg.kv_head * p.num_pages * Q3_PAGE;
+            uint32_t tile = seg.tile_begin;
+
+            /* Key tiles of the shared prefix whose 128 keys every row sees: no
+             * mask data, and the page ids of the next tile are fetched while
+             * this tile's loads are armed. This loop sets the pace of the whole
+             * CTA when it is slow: with the general code below for every tile
+             * the producer needed 3.5 k clocks per key tile (page-id load,
+             * run lookup and mask summary between two tiles' loads), more than
+             * the softmax threads. */
+            const uint32_t fast_end = min(seg.tile_end, min(seg.shared_tiles, p.shared_len >> 7));
+            uint32_t pg = 0;
+            if (tile < fast_end && lane < 8) pg = p.page_ids[tile * 8 + lane];
+            for (; tile < fast_end; tile++) {
+                const int32_t row = (int32_t)(row_base + pg * Q3_PAGE);
+                const uint32_t pg0 = __shfl_sync(0xffffffffu, pg, 0);
+                const bool run = __all_sync(0xffffffffu, lane >= 8 || pg == pg0 + lane);
+                if (tile + 1 < fast_end && lane < 8) pg = p.page_ids[(tile + 1) * 8 + lane];
+                alive = wait_or_abort(&bar.k_empty[it % kStages], ((it / kStages) & 1u) ^ 1u, misc);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                if (lane == 0) misc->meta[it % kMetaRing].nomask = 1u;
+                arm_tile(row, run);
+                if (!alive) break;
+            }
+            if (!alive) break;
+
+            /* The remaining tiles: a partly filled shared page, the branches'
+             * own pages. Lanes 0..7 resolve one page slot each. */
+            for (; tile < seg.tile_end; tile++) {
                 uint32_t kind = kSlotInvalid, tag = 0, base = 0, nvis = 0;
                 uint32_t page = 0;
                 if (lane < 8) {
@@ -373,13 +445,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     (kind == kSlotPrivate && uniform && tag == first_tag &&
                      base + 15u <= min_lp);
                 const uint32_t whole_mask = __ballot_sync(0xffffffffu, whole) & 0xFFu;
-                const int32_t row =
-                    kind == kSlotInvalid
-                        ? (int32_t)p.pool_rows_total
-                        : (int32_t)(p.pool_row_base +
-                                    (seg.kv_head * p.num_pages + page) * Q3_PAGE);
-
-                alive = wait_or_abort(&bar.k_empty[stage], ph ^ 1u, misc);
+                const int32_t row = kind == kSlotInvalid ? (int32_t)p.pool_rows_total
+                                                         : (int32_t)(row_base + page * Q3_PAGE);
+                alive = wait_or_abort(&bar.k_empty[it % kStages], ((it / kStages) & 1u) ^ 1u, misc);
                 alive = __all_sync(0xffffffffu, alive);
                 if (!alive) break;
                 TileMeta &m = misc->meta[it % kMetaRing];
@@ -389,28 +457,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     m.base[lane] = base;
                     m.nvis[lane] = nvis;
                 }
-                if (lane == 0) {
-                    m.nomask = whole_mask == 0xFFu;
-                    mbar_arrive_expect_tx(&bar.k_full[stage], kTileBytes);
-                }
-                __syncwarp();
-                if (lane < 8) {
-                    uint8_t *dst = smem + kSmemK + stage * kTileBytes + lane * kPageHalfBytes;
-                    tma_load_2d(dst, &k_map, 0, row, &bar.k_full[stage]);
-                    tma_load_2d(dst + kHalfBytes, &k_map, 64, row, &bar.k_full[stage]);
-                }
-                it++;
-                alive = wait_or_abort(&bar.v_empty[stage], ph ^ 1u, misc);
-                alive = __all_sync(0xffffffffu, alive);
+                if (lane == 0) m.nomask = whole_mask == 0xFFu;
+                arm_tile(row, false);
                 if (!alive) break;
-                if (lane == 0) mbar_arrive_expect_tx(&bar.v_full[stage], kTileBytes);
-                __syncwarp();
-                if (lane < 8) {
-                    uint8_t *dst = smem + kSmemV + stage * kTileBytes + lane * kPageHalfBytes;
-                    tma_load_2d(dst, &v_map, 0, row, &bar.v_full[stage]);
-                    tma_load_2d(dst + kHalfBytes, &v_map, 64, row, &bar.v_full[stage]);
-                }
-                v_armed++;
             }
         }
         if (!alive && lane == 0) {
@@ -896,8 +945,8 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st
     p.fix_counters = rt->fix_counters;
     p.status = rt->status_dev;
     q3_phase_begin(rt, Q3_PHASE_ATTENTION);
-    attention_tc_kernel<<<st->grid, kThreads, kSmemTotal, rt->stream>>>(q_map, rt->k_map,
-                                                                       rt->v_map, p);
+    attention_tc_kernel<<<st->grid, kThreads, kSmemTotal, rt->stream>>>(
+        q_map, rt->k_map, rt->v_map, rt->k_map_tile, rt->v_map_tile, p);
     q3_phase_end(rt);
     Q3_LAUNCH_CHECK("attention_tc launch failed");
     rt->n_launch++;

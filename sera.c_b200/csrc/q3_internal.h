@@ -64,6 +64,8 @@ struct q3_attn_runtime {
     __half *v_pool;
     CUtensorMap k_map; /* 2-D {128, L*Hkv*num_pages*16}, box {64,16}, SW128 */
     CUtensorMap v_map;
+    CUtensorMap k_map_tile; /* same tensors, box {64,128}: eight consecutive pages in one copy */
+    CUtensorMap v_map_tile;
     std::vector<uint32_t> free_pages;
 
     float *qk_norm_w;  /* device [L][2][128] */

@@ -272,6 +272,10 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
     if (!q3_encode_tmap_2d(&rt->k_map, rt->k_pool, Q3_D, pool_rows, 64, Q3_PAGE, error,
                            error_len) ||
         !q3_encode_tmap_2d(&rt->v_map, rt->v_pool, Q3_D, pool_rows, 64, Q3_PAGE, error,
+                           error_len) ||
+        !q3_encode_tmap_2d(&rt->k_map_tile, rt->k_pool, Q3_D, pool_rows, 64, 8 * Q3_PAGE, error,
+                           error_len) ||
+        !q3_encode_tmap_2d(&rt->v_map_tile, rt->v_pool, Q3_D, pool_rows, 64, 8 * Q3_PAGE, error,
                            error_len)) {
         q3_attn_destroy(rt);
         return NULL;
