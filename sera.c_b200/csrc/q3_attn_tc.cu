@@ -388,29 +388,45 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             const uint32_t row_base = p.pool_row_base + seg.kv_head * p.num_pages * Q3_PAGE;
             uint32_t tile = seg.tile_begin;
 
-            /* Key tiles of the shared prefix whose 128 keys every row sees: no
-             * mask data, and the page ids of the next tile are fetched while
-             * this tile's loads are armed. This loop sets the pace of the whole
-             * CTA when it is slow: with the general code below for every tile
-             * the producer needed 3.5 k clocks per key tile (page-id load,
-             * run lookup and mask summary between two tiles' loads), more than
-             * the softmax threads. */
-            const uint32_t fast_end = min(seg.tile_end, min(seg.shared_tiles, p.shared_len >> 7));
-            uint32_t pg = 0;
-            if (tile < fast_end && lane < 8) pg = p.page_ids[tile * 8 + lane];
-            for (; tile < fast_end; tile++) {
-                const int32_t row = (int32_t)(row_base + pg * Q3_PAGE);
-                const uint32_t pg0 = __shfl_sync(0xffffffffu, pg, 0);
-                const bool run = __all_sync(0xffffffffu, lane >= 8 || pg == pg0 + lane);
-                if (tile + 1 < fast_end && lane < 8) pg = p.page_ids[(tile + 1) * 8 + lane];
-                alive = wait_or_abort(&bar.k_empty[it % kStages], ((it / kStages) & 1u) ^ 1u, misc);
-                alive = __all_sync(0xffffffffu, alive);
-                if (!alive) break;
-                if (lane == 0) misc->meta[it % kMetaRing].nomask = 1u;
-                arm_tile(row, run);
+            /* Key tiles whose 128 keys every row of the item sees: no mask data,
+             * and the page ids of the next tile are fetched while this tile's
+             * loads are armed. This loop sets the pace of the whole CTA when it
+             * is slow: with the general code below for every tile the producer
+             * needed 3.5 k clocks per key tile (page-id load, run lookup and
+             * mask summary between two tiles' loads), more than the softmax
+             * threads. Tiles [tile, fend) take their pages from
+             * page_ids[table + (tile - t_off) * 8 ...]. */
+            auto fast_tiles = [&](uint32_t fend, uint32_t table, uint32_t t_off) {
+                uint32_t pg = 0;
+                if (tile < fend && lane < 8) pg = p.page_ids[table + (tile - t_off) * 8 + lane];
+                for (; tile < fend; tile++) {
+                    const int32_t row = (int32_t)(row_base + pg * Q3_PAGE);
+                    const uint32_t pg0 = __shfl_sync(0xffffffffu, pg, 0);
+                    const bool run = __all_sync(0xffffffffu, lane >= 8 || pg == pg0 + lane);
+                    if (tile + 1 < fend && lane < 8)
+                        pg = p.page_ids[table + (tile + 1 - t_off) * 8 + lane];
+                    alive = wait_or_abort(&bar.k_empty[it % kStages], ((it / kStages) & 1u) ^ 1u,
+                                          misc);
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) return;
+                    if (lane == 0) misc->meta[it % kMetaRing].nomask = 1u;
+                    arm_tile(row, run);
+                    if (!alive) return;
+                }
+            };
+            /* the shared prefix, up to its last full tile */
+            fast_tiles(min(seg.tile_end, min(seg.shared_tiles, p.shared_len >> 7)), 0u, 0u);
+            if (!alive) break;
+            /* an item of one branch (a causal prefill chunk, a long suffix): its own
+             * keys below the first row's position */
+            if (tile >= seg.shared_tiles && seg.run_end == seg.run_begin + 1 && uniform) {
+                const q3_run run = p.runs[seg.run_begin];
+                if (run.tag == first_tag && min_lp != 0xFFFFFFFFu)
+                    fast_tiles(min(seg.tile_end,
+                                   seg.shared_tiles + min((min_lp + 1u) >> 7, run.n_pages >> 3)),
+                               run.table_off, seg.shared_tiles);
                 if (!alive) break;
             }
-            if (!alive) break;
 
             /* The remaining tiles: a partly filled shared page, the branches'
              * own pages. Lanes 0..7 resolve one page slot each. */
