@@ -30,8 +30,10 @@
  *               MN-major), D = O in tensor memory (fp32).
  *   TMEM        S [0,128), P0 [128,192), P1 [192,256), O0 [256,384), O1 [384,512).
  *   K/V pages   4 KiB per page per head, fetched by TMA (two 64-column boxes,
- *               128-byte swizzle) straight into the UMMA operand layout. Every
- *               CTA issues its own loads, from this GPU's memory only.
+ *               128-byte swizzle) straight into the UMMA operand layout; the
+ *               eight pages of a key tile as two 128-row boxes when they follow
+ *               one another in the pool. Every CTA issues its own loads, from
+ *               this GPU's memory only.
  * Warp roles: 0 = TMA producer, 1 = issuer of the S MMAs (owns the TMEM
  * allocation), 2 / 3 = issuers of the PV MMAs of M tile 0 / 1 (three threads
  * issue, each waiting on its own events in order, so that no event waits
@@ -44,7 +46,8 @@
  * partials plus (max, sum) and bumps an arrival counter per 32 rows; the warp
  * that arrives last combines all pieces of its rows with log-sum-exp (its own
  * partial straight from tensor memory) and writes them. No CTA waits for
- * another.
+ * another. A piece's O is stored lane-interleaved, so that the writer's and the
+ * combining warp's accesses are 512 contiguous bytes per warp.
  *
  * Every mbarrier wait is bounded; on expiry the thread raises a flag in shared
  * memory, the status word is set and all roles leave; the producer first
