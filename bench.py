@@ -626,6 +626,75 @@ def case_q4k_linear(pkg, torch, device, M=2048, N=(H + 2 * HKV) * D, K=5120, rep
                                 / peaks["hbm_gbs"]}
 
 
+def case_qkv_fused(pkg, torch, device, T=4096, K=5120, reps=20):
+    """Prefill of T tokens of one layer starting from the layer's input rows:
+    the three Q4_K projections + norm/RoPE/KV-write kernel + attention (the
+    sequence of the reference's run_layer with this library's kernels) against
+    the projection whose epilogue does the norm, the rotation and the page write
+    (q3_prefix_prefill_layer_projected: two launches, no q/k/v tensors). Weights
+    in the tiled order, three weight sets cycled so that they come from HBM."""
+    from sera_c_b200 import q4_linear
+    lin = q4_linear.Q4Linear(device.index, T, H * D, K)
+    sets = []
+    for i in range(3):
+        ws, geos = [], []
+        for j, n in enumerate((H, HKV, HKV)):
+            geo = q4_linear.bind_geometry(K, n * D)
+            t, tgeo = lin.pack(geo, random_q4k_weight(torch, n * D, K, device, seed=10 * i + j))
+            ws.append(t)
+            geos.append(tgeo)
+        sets.append((ws, geos, pkg.qkv_weights(ws[0], ws[1], ws[2], K, geos[0].qtype)))
+    g = torch.Generator(device=device).manual_seed(1)
+    x = (torch.randn(T, K, generator=g, device=device) * 0.02).to(torch.float16)
+    rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=HKV, max_positions=T,
+                     max_tokens=T, num_pages=T // 16 + 4, device=device.index)
+    rt.enable_timing(32 * reps + 64)
+    prefix = pkg.Prefix(rt, T)
+    q = torch.empty(T, H, D, dtype=torch.bfloat16, device=device)
+    k = torch.empty(T, HKV, D, dtype=torch.bfloat16, device=device)
+    v = torch.empty(T, HKV, D, dtype=torch.bfloat16, device=device)
+    out_a = torch.zeros(T, H, D, dtype=torch.bfloat16, device=device)
+    out_b = torch.zeros(T, H, D, dtype=torch.bfloat16, device=device)
+    stream = rt.stream_ptr
+    it = [0]
+
+    def unfused():
+        ws, geos, _ = sets[it[0] % 3]
+        it[0] += 1
+        for w, geo, o in zip(ws, geos, (q, k, v)):
+            lin.linear_f16(geo, w, x, out=o.view(T, -1), stream=stream)
+        prefix.prefill_layer(0, q, k, v, out_a)
+
+    def fused():
+        _, _, W = sets[it[0] % 3]
+        it[0] += 1
+        prefix.prefill_layer_projected(0, W, x, out_b)
+
+    ms_u, _ = _time_calls(torch, rt, unfused, reps)
+    ms_f, ph = _time_calls(torch, rt, fused, reps)
+    it[0] = 0
+    unfused()
+    it[0] = 0
+    fused()
+    torch.cuda.synchronize()
+    diff = float((out_a.float() - out_b.float()).abs().max())
+    flops = 2.0 * T * (H + 2 * HKV) * D * K + 4 * D * H * (T * (T + 1) // 2)
+    res = {"tokens": T, "hidden": K, "unfused_ms": ms_u, "fused_ms": ms_f,
+           "speedup": ms_u / ms_f, "fused_tflops": flops / ms_f / 1e9,
+           "fused_projection_kernel_ms": ph["kvwrite"][0] / max(ph["kvwrite"][1], 1),
+           "attention_kernel_ms": ph["attention"][0] / max(ph["attention"][1], 1),
+           "max_abs_diff_between_the_two_paths": diff,
+           "launches_per_layer": {"unfused": 5, "fused": 2},
+           "status": lin.status()}
+    prefix.close()
+    rt.close()
+    return res
+
+
+CASES["qkv_fused_prefill_4096"] = lambda pkg, torch, dev, reps: case_qkv_fused(pkg, torch, dev, 4096, reps=reps)
+CASES["qkv_fused_prefill_2048"] = lambda pkg, torch, dev, reps: case_qkv_fused(pkg, torch, dev, 2048, reps=reps)
+
+
 CASES.update({
     "q4k_qkv_2048": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 2048, reps=reps),
     "q4k_qkv_4096": lambda pkg, torch, dev, reps: case_q4k_linear(pkg, torch, dev, 4096, reps=reps),

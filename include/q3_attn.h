@@ -504,6 +504,36 @@ bool q3_suffix_attention_layer_gathered_host(q3_pack_plan *plan, uint32_t layer,
                                              void *out_host, char *error,
                                              size_t error_len);
 
+/* --- the layer with its q/k/v projection fused in ------------------------- *
+ * The reference's layer drivers run three quantised linears, then rms_norm on
+ * q and k, rope, and the KV append or scatter (ref: src/q3_forward.cu:1214-1278
+ * and :1462-1516): q, k and v are written by the linears and read again by the
+ * next five steps. Here the projection's epilogue normalises, rotates and
+ * writes - queries as f16 into the attention kernel's Q buffer, keys and values
+ * into their pages - so q, k and v never exist as tensors: two launches per
+ * layer (projection, attention).
+ *   weights  three resident Q4_K tensors [heads*128][hidden], all in the GGUF
+ *            order (Q3_QUANT_Q4_K = 12) or all in the tiled order of
+ *            q3_cuda_q4k_linear_pack (include/q3_q4_linear.h); other types are
+ *            refused with a message - project them with q3_cuda_q4k_linear_f16
+ *            and call the plain layer entry;
+ *   x_f16    the layer's input rows after the attention norm, f16
+ *            [tokens][hidden], device memory, 16-byte aligned;
+ * everything else as q3_prefix_prefill_layer / q3_suffix_attention_layer.
+ * q3_cuda_q4k_linear_init must have been called on this device. */
+typedef struct {
+    const void *wq, *wk, *wv;
+    uint32_t qtype_q, qtype_k, qtype_v;
+    uint32_t hidden;
+} q3_qkv_weights;
+bool q3_prefix_prefill_layer_projected(q3_prefix_kv *prefix, uint32_t layer,
+                                       const q3_qkv_weights *weights, const void *x_f16,
+                                       uint32_t tokens, void *out, char *error,
+                                       size_t error_len);
+bool q3_suffix_attention_layer_projected(q3_pack_plan *plan, uint32_t layer,
+                                         const q3_qkv_weights *weights, const void *x_f16,
+                                         void *out, char *error, size_t error_len);
+
 /* --- diagnostics: the launch schedule (pure host, no CUDA) ---------------- *
  * The tensor-core attention kernel is launched with one CTA per SM; the host
  * cuts the launch into segments = (32-token tile, KV head, range of 128-key

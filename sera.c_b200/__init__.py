@@ -28,6 +28,18 @@ def _u32(a):
     return a, a.ctypes.data_as(_c_u32p)
 
 
+def qkv_weights(wq, wk, wv, hidden, qtype=12):
+    """q3_qkv_weights for the *_projected layer entries: three resident
+    quantised weights (torch uint8 tensors on the device), one type for all
+    (12 = Q4_K in GGUF order, 12 | 1 << 16 = the tiled order)."""
+    w = _lib.QkvWeights()
+    w.wq, w.wk, w.wv = wq.data_ptr(), wk.data_ptr(), wv.data_ptr()
+    w.qtype_q = w.qtype_k = w.qtype_v = qtype
+    w.hidden = hidden
+    w._keep = (wq, wk, wv)
+    return w
+
+
 def _ptr(t):
     """Device pointer of a torch tensor (or None)."""
     if t is None:
@@ -239,6 +251,12 @@ class Prefix:
         _call(lib().q3_prefix_prefill_layer, self.h, layer, _ptr(q), _ptr(k), _ptr(v),
               q.shape[0], _ptr(out))
 
+    def prefill_layer_projected(self, layer, weights, x_f16, out):
+        """q/k/v projection (three resident Q4_K weights) with norm + RoPE + page
+        write as its epilogue, then attention. `weights`: qkv_weights(...)."""
+        _call(lib().q3_prefix_prefill_layer_projected, self.h, layer, ctypes.byref(weights),
+              _ptr(x_f16), x_f16.shape[0], _ptr(out))
+
     def advance(self, tokens):
         _call(lib().q3_prefix_advance, self.h, tokens)
 
@@ -365,6 +383,12 @@ class PackPlan:
     def attention_layer(self, layer, q, k, v, out):
         _call(lib().q3_suffix_attention_layer, self.h, layer, _ptr(q), _ptr(k), _ptr(v),
               _ptr(out))
+
+    def attention_layer_projected(self, layer, weights, x_f16, out):
+        """The layer with its q/k/v projection fused in (see
+        Prefix.prefill_layer_projected)."""
+        _call(lib().q3_suffix_attention_layer_projected, self.h, layer, ctypes.byref(weights),
+              _ptr(x_f16), _ptr(out))
 
     def attention_layer_gathered(self, layer, q, k, v, peers, seq):
         """Attention fused with the output all-gather: `peers` is a GatherPeers

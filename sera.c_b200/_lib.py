@@ -20,6 +20,13 @@ class LinearGeometry(ctypes.Structure):
                 ("qtype", ctypes.c_uint32), ("weight_bytes", ctypes.c_uint64)]
 
 
+class QkvWeights(ctypes.Structure):
+    """q3_qkv_weights"""
+    _fields_ = [("wq", ctypes.c_void_p), ("wk", ctypes.c_void_p), ("wv", ctypes.c_void_p),
+                ("qtype_q", ctypes.c_uint32), ("qtype_k", ctypes.c_uint32),
+                ("qtype_v", ctypes.c_uint32), ("hidden", ctypes.c_uint32)]
+
+
 class LinearStats(ctypes.Structure):
     """q3_q4_linear_stats"""
     _fields_ = [("total_ms", ctypes.c_double), ("activation_quant_ms", ctypes.c_double),
@@ -173,6 +180,10 @@ def bind(AttnConfig, AttnStats, SuffixItem, SchedSegmentInfo, SchedSummary):
     sig("q3_pack_plan_branch_offsets", up, [vp])
     sig("q3_suffix_attention_layer", b, [vp, u32, vp, vp, vp, vp] + err)
     sig("q3_suffix_attention_layer_host", b, [vp, u32, vp, vp, vp, vp] + err)
+    sig("q3_suffix_attention_layer_projected", b,
+        [vp, u32, ctypes.POINTER(QkvWeights), vp, vp] + err)
+    sig("q3_prefix_prefill_layer_projected", b,
+        [vp, u32, ctypes.POINTER(QkvWeights), vp, u32, vp] + err)
     sig("q3_suffix_attention_layer_gathered_host", b,
         [vp, u32, vp, vp, vp, ctypes.POINTER(GatherPeers), u32, vp] + err)
     sig("q3_suffix_attention_layer_gathered", b,

@@ -260,6 +260,25 @@ bool q3_launch_decode(q3_attn_runtime *rt, uint32_t layer,
 
 bool q3_prepare_attention_kernel(char *error, size_t error_len);
 bool q3_prepare_decode_kernel(char *error, size_t error_len);
+/* q3_q4k_linear.cu: the q/k/v projection with norm + RoPE + page write as its
+ * epilogue. All pointers are device pointers. */
+struct q3_qkv_fused_args {
+    const void *wq, *wk, *wv;   /* [n_q_heads*128][hidden], [n_kv_heads*128][hidden] x 2 */
+    uint32_t qtype;             /* Q4_K in GGUF or tiled order, the same for all three */
+    uint32_t hidden;
+    uint32_t n_q_heads, n_kv_heads;
+    const void *x_f16;          /* [tokens][hidden] */
+    uint32_t tokens;
+    const float *norm_w;        /* [2][128] of the layer */
+    float eps;
+    const void *rope_table;     /* float2 [position][64] */
+    const uint32_t *rope_pos, *dst_page, *dst_slot;
+    void *q_out;                /* f16 [tokens][n_q_heads][128] */
+    void *k_pool, *v_pool;      /* the layer's pages: f16 [kv head][page][16][128] */
+    uint32_t num_pages;
+};
+bool q3_launch_qkv_fused(const q3_qkv_fused_args *a, cudaStream_t stream, char *error,
+                         size_t error_len);
 bool q3_prepare_kvwrite_kernel(char *error, size_t error_len);
 
 /* Entry points make the runtime's device current: a host that drives several

@@ -80,15 +80,19 @@ constexpr uint32_t kColA = 256;                    /* A stage: 128 lanes x 32 co
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSmemX = 0;
 constexpr uint32_t kSmemRaw = kSmemX + kXStages * kXStageBytes;
-template <uint32_t QT>
+constexpr uint32_t kStageTokens = 16;               /* fused epilogue: tokens staged per group */
+constexpr uint32_t kStageBytes = kStageTokens * 128 * 4;
+template <uint32_t QT, bool FUSED = false>
 struct Smem {
     static constexpr uint32_t kRowBytes = Fmt<QT>::kRowBytes;
     static constexpr uint32_t kRawBytes = 128 * kRowBytes;   /* 128 feature rows, one block each */
     static constexpr uint32_t kTiledRows = kRawBytes / 256;  /* tiled layout: a chunk in rows of 256 B */
-    static constexpr uint32_t kMisc = kSmemRaw + kRawStages * kRawBytes;
-    static constexpr uint32_t kTotal = kMisc + 256 + 1024;   /* + alignment slack */
+    static constexpr uint32_t kStage = kSmemRaw + kRawStages * kRawBytes;  /* fused epilogue only */
+    static constexpr uint32_t kMisc = kStage + (FUSED ? kGroups * kStageBytes : 0u);
+    static constexpr uint32_t kTotal = kMisc + 512 + 1024;   /* + alignment slack */
 };
 static_assert(Smem<6>::kTotal <= 227 * 1024, "shared memory budget");
+static_assert(Smem<4, true>::kTotal <= 227 * 1024, "shared memory budget of the fused kernel");
 static_assert(kColA + kAStages * 32 <= kTmemCols, "tensor memory budget");
 static_assert(kAStages % kGroups == 0, "a group must come back to its own stages");
 
@@ -97,10 +101,28 @@ struct Misc {
     uint64_t x_full[kXStages], x_empty[kXStages];
     uint64_t a_full[kAStages], a_empty[kAStages];
     uint64_t acc_full, d_free;
+    uint64_t stage_full[kGroups], stage_empty[kGroups];   /* fused epilogue: staging hand-over */
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
-static_assert(sizeof(Misc) <= 256, "Misc must fit its slot");
+static_assert(sizeof(Misc) <= 512, "Misc must fit its slot");
+
+/* Fused epilogue of the q/k/v projection (ref: the five steps after the three
+ * linears in run_layer / run_layer_packed, src/q3_forward.cu:1244-1278 and
+ * :1489-1516): a feature tile of 128 is one head; query and key heads are
+ * RMS-normalised and rotated, all three are written as f16 - queries into the
+ * attention kernel's Q buffer, keys and values into their pages. */
+struct FusedEpilogue {
+    uint32_t seg_end[3];      /* feature tiles: [0, e0) query heads, [e0, e1) key, [e1, e2) value */
+    uint32_t n_q_heads;
+    const float *norm_w;      /* [2][128]: query weights, key weights */
+    float eps;
+    const float2 *rope_table; /* [position][64] (cos, sin) of the pair (d, d + 64) */
+    const uint32_t *rope_pos, *dst_page, *dst_slot;
+    __half *q_out;            /* [tokens][n_q_heads][128] */
+    __half *k_pool, *v_pool;  /* this layer: [kv head][page][16][128] */
+    uint32_t num_pages;
+};
 
 struct LinearParams {
     void *out;
@@ -109,6 +131,7 @@ struct LinearParams {
     uint32_t w_tiled;     /* weight in the tiled layout of q3_cuda_q4k_linear_pack */
     uint32_t out_type;
     uint32_t *status;
+    FusedEpilogue f;      /* read by the fused instantiation only */
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, Misc *misc) {
@@ -265,16 +288,18 @@ __device__ __forceinline__ void store_chunk(const LinearParams &p, const uint32_
  * waits until every thread has read the previous tile's D out of tensor
  * memory (d_free). A group reads D after it has already converted its next two
  * k-steps, so the MMA has operands to go on with while the rows are stored. */
-template <uint32_t QT>
+template <uint32_t QT, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
 q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
-                     const __grid_constant__ CUtensorMap w_map, const LinearParams p) {
+                     const __grid_constant__ CUtensorMap w_map,
+                     const __grid_constant__ CUtensorMap w_map1,
+                     const __grid_constant__ CUtensorMap w_map2, const LinearParams p) {
     constexpr uint32_t kRawRowBytes = Smem<QT>::kRowBytes;
     constexpr uint32_t kRawBytes = Smem<QT>::kRawBytes;
     constexpr uint32_t kTiledRows = Smem<QT>::kTiledRows;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    Misc *misc = reinterpret_cast<Misc *>(smem + Smem<QT>::kMisc);
+    Misc *misc = reinterpret_cast<Misc *>(smem + Smem<QT, FUSED>::kMisc);
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t n_super = p.K / Q3_QUANT_QK_K;   /* Q4_K blocks per feature row */
@@ -299,6 +324,10 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
         }
         mbar_init(&misc->acc_full, 1);
         mbar_init(&misc->d_free, 128 * kGroups);
+        for (uint32_t s = 0; s < kGroups; s++) {
+            mbar_init(&misc->stage_full[s], 128);
+            mbar_init(&misc->stage_empty[s], 128);
+        }
         misc->abort_flag = 0;
         fence_mbar_init();
     }
@@ -335,11 +364,26 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
         /* ============ raw Q4_K blocks ============ */
         if (lane == 0) {
             prefetch_tmap(&w_map);
+            if (FUSED) {
+                prefetch_tmap(&w_map1);
+                prefetch_tmap(&w_map2);
+            }
             bool alive = true;
             uint32_t g = 0;   /* super-blocks issued so far */
             for (uint32_t ti = 0; ti < n_my && alive; ti++) {
                 const uint32_t tile = blockIdx.x + ti * gridDim.x;
-                const uint32_t n0 = (tile / n_tok_tiles) * 128u;
+                uint32_t ft = tile / n_tok_tiles;      /* feature tile */
+                const CUtensorMap *wm = &w_map;
+                if (FUSED) {                           /* q, k and v are three tensors */
+                    if (ft >= p.f.seg_end[1]) {
+                        wm = &w_map2;
+                        ft -= p.f.seg_end[1];
+                    } else if (ft >= p.f.seg_end[0]) {
+                        wm = &w_map1;
+                        ft -= p.f.seg_end[0];
+                    }
+                }
+                const uint32_t n0 = ft * 128u;
                 for (uint32_t sb = 0; sb < n_super; sb++, g++) {
                     const uint32_t rs = g % kRawStages, use = g / kRawStages;
                     if (use > 0)
@@ -347,11 +391,11 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
                     if (!alive) break;
                     mbar_arrive_expect_tx(&misc->raw_full[rs], kRawBytes);
                     if (p.w_tiled)   /* 18432 contiguous bytes = 72 rows of 256 */
-                        tma_load_2d(smem + kSmemRaw + rs * kRawBytes, &w_map, 0,
+                        tma_load_2d(smem + kSmemRaw + rs * kRawBytes, wm, 0,
                                     (int32_t)(((n0 / 128u) * n_super + sb) * kTiledRows),
                                     &misc->raw_full[rs]);
                     else
-                        tma_load_2d(smem + kSmemRaw + rs * kRawBytes, &w_map,
+                        tma_load_2d(smem + kSmemRaw + rs * kRawBytes, wm,
                                     (int32_t)(sb * kRawRowBytes), (int32_t)n0,
                                     &misc->raw_full[rs]);
                 }
@@ -414,8 +458,125 @@ q4k_linear_tc_kernel(const __grid_constant__ CUtensorMap x_map,
             }
         };
 
+        /* Fused epilogue: the group's 32-token chunks of D go through a staging
+         * buffer of 16 tokens x 128 features (fp32) so that a warp can work
+         * along a token's head: lane l holds features 2l, 2l+1, 64+2l, 65+2l -
+         * both members of two rotary pairs. Arithmetic per row as in the
+         * stand-alone kernel (q3_kvwrite.cu), on the fp32 accumulator instead
+         * of a bf16 copy of it. */
+        uint32_t stage_use = 0;
+        auto drain_fused = [&](uint32_t ti) {
+            publish();
+            if (alive) alive = wait_or_abort(&misc->acc_full, ti & 1u, misc);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) return;
+            tc_fence_after();
+            const uint32_t tile = blockIdx.x + ti * gridDim.x;
+            const uint32_t m0 = (tile % n_tok_tiles) * p.NT;
+            uint32_t head = tile / n_tok_tiles, kind = 0;     /* 0 query, 1 key, 2 value */
+            if (head >= p.f.seg_end[1]) {
+                kind = 2;
+                head -= p.f.seg_end[1];
+            } else if (head >= p.f.seg_end[0]) {
+                kind = 1;
+                head -= p.f.seg_end[0];
+            }
+            float2 w_lo = make_float2(1.f, 1.f), w_hi = make_float2(1.f, 1.f);
+            if (kind < 2) {
+                w_lo = *reinterpret_cast<const float2 *>(p.f.norm_w + kind * 128u + 2u * lane);
+                w_hi = *reinterpret_cast<const float2 *>(p.f.norm_w + kind * 128u + 64u + 2u * lane);
+            }
+            float *stg = reinterpret_cast<float *>(smem + Smem<QT, FUSED>::kStage +
+                                                   group * kStageBytes);
+            const uint32_t wig = warp & 3u;      /* warp within the group */
+            bool released = false;
+            for (uint32_t ch = group; ch < n_chunks && alive; ch += kGroups) {
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + kColD + ch * 32u, v);
+                tmem_wait_ld();
+                if (ch + kGroups >= n_chunks) {      /* last chunk of this thread: release D */
+                    tc_fence_before();
+                    mbar_arrive(&misc->d_free);
+                    released = true;
+                }
+#pragma unroll
+                for (uint32_t hf = 0; hf < 2; hf++) {
+                    /* this warp's four tokens: position and page, in flight during
+                     * the staging hand-over below */
+                    uint32_t pos[4], page[4], slot[4];
+#pragma unroll
+                    for (uint32_t tt = 0; tt < 4; tt++) {
+                        const uint32_t tl = ch * 32u + hf * kStageTokens + wig * 4u + tt;
+                        const uint32_t token = m0 + tl;
+                        const bool ok = tl < p.NT && token < p.M;
+                        pos[tt] = ok && kind < 2 ? p.f.rope_pos[token] : 0u;
+                        page[tt] = ok ? (kind ? p.f.dst_page[token] : 0u) : Q3_NO_PAGE;
+                        slot[tt] = ok && kind ? p.f.dst_slot[token] : 0u;
+                    }
+                    if (stage_use > 0)
+                        alive = wait_or_abort(&misc->stage_empty[group], (stage_use - 1u) & 1u, misc);
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+#pragma unroll
+                    for (uint32_t i = 0; i < kStageTokens; i++)
+                        stg[i * 128u + row] = __uint_as_float(v[hf * kStageTokens + i]);
+                    mbar_arrive(&misc->stage_full[group]);
+                    alive = wait_or_abort(&misc->stage_full[group], stage_use & 1u, misc);
+                    alive = __all_sync(0xffffffffu, alive);
+                    if (!alive) break;
+                    float4 cs[4];
+                    if (kind < 2) {
+#pragma unroll
+                        for (uint32_t tt = 0; tt < 4; tt++)
+                            cs[tt] = *reinterpret_cast<const float4 *>(
+                                p.f.rope_table + (size_t)pos[tt] * 64u + 2u * lane);
+                    }
+#pragma unroll
+                    for (uint32_t tt = 0; tt < 4; tt++) {
+                        const uint32_t t16 = wig * 4u + tt;
+                        float2 a = *reinterpret_cast<const float2 *>(stg + t16 * 128u + 2u * lane);
+                        float2 b = *reinterpret_cast<const float2 *>(stg + t16 * 128u + 64u + 2u * lane);
+                        if (kind < 2) {
+                            float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+#pragma unroll
+                            for (uint32_t o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                            const float inv = 1.0f / sqrtf(ss * (1.0f / 128.0f) + p.f.eps);
+                            /* x' = x * inv * w;  (a, b) -> (a c - b s, a s + b c) */
+                            const float ax = a.x * inv * w_lo.x, ay = a.y * inv * w_lo.y;
+                            const float bx = b.x * inv * w_hi.x, by = b.y * inv * w_hi.y;
+                            a.x = fmaf(ax, cs[tt].x, -bx * cs[tt].y);
+                            b.x = fmaf(ax, cs[tt].y, bx * cs[tt].x);
+                            a.y = fmaf(ay, cs[tt].z, -by * cs[tt].w);
+                            b.y = fmaf(ay, cs[tt].w, by * cs[tt].z);
+                        }
+                        if (page[tt] != Q3_NO_PAGE) {
+                            const uint32_t token = m0 + ch * 32u + hf * kStageTokens + t16;
+                            __half *dst =
+                                kind == 0
+                                    ? p.f.q_out + ((size_t)token * p.f.n_q_heads + head) * 128u
+                                    : (kind == 1 ? p.f.k_pool : p.f.v_pool) +
+                                          (((size_t)head * p.f.num_pages + page[tt]) * Q3_PAGE +
+                                           slot[tt]) * 128u;
+                            *reinterpret_cast<__half2 *>(dst + 2u * lane) = __floats2half2_rn(a.x, a.y);
+                            *reinterpret_cast<__half2 *>(dst + 64u + 2u * lane) = __floats2half2_rn(b.x, b.y);
+                        }
+                    }
+                    mbar_arrive(&misc->stage_empty[group]);
+                    stage_use++;
+                }
+            }
+            if (!released) {
+                tc_fence_before();
+                mbar_arrive(&misc->d_free);
+            }
+        };
+
         /* Read this thread's share of tile ti's D, release D, store the rows. */
         auto drain = [&](uint32_t ti) {
+            if (FUSED) {
+                drain_fused(ti);
+                return;
+            }
             publish();
             if (alive) alive = wait_or_abort(&misc->acc_full, ti & 1u, misc);
             alive = __all_sync(0xffffffffu, alive);
@@ -604,7 +765,7 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
                                    error_len);
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g.device);
-    LinearParams p;
+    LinearParams p = {};
     p.out = out;
     p.M = M;
     p.N = N;
@@ -630,14 +791,80 @@ bool launch_linear(const q3_q4_linear_geometry *geo, const void *weight, const v
     const uint32_t n_tiles = ((M + p.NT - 1) / p.NT) * (N / 128);
     const uint32_t grid = n_tiles < (uint32_t)sms ? n_tiles : (uint32_t)sms;
     if (q6)
-        q4k_linear_tc_kernel<6><<<grid, kThreads, Smem<6>::kTotal, stream>>>(x_map, w_map, p);
+        q4k_linear_tc_kernel<6, false><<<grid, kThreads, Smem<6>::kTotal, stream>>>(
+            x_map, w_map, w_map, w_map, p);
     else
-        q4k_linear_tc_kernel<4><<<grid, kThreads, Smem<4>::kTotal, stream>>>(x_map, w_map, p);
+        q4k_linear_tc_kernel<4, false><<<grid, kThreads, Smem<4>::kTotal, stream>>>(
+            x_map, w_map, w_map, w_map, p);
     Q3_LAUNCH_CHECK("q4k_linear_tc launch failed");
     return true;
 }
 
 }  // namespace
+
+/* The q/k/v projection with the norm + rotation + page write as its epilogue:
+ * one launch over the feature tiles of the three weights (Q4_K, all in the
+ * GGUF order or all in the tiled order), a head per tile. */
+bool q3_launch_qkv_fused(const q3_qkv_fused_args *a, cudaStream_t stream, char *error,
+                         size_t error_len) {
+    if (!g.initialized)
+        return q3_fail(error, error_len, "q3_q4_linear: not initialized");
+    if (a->qtype != Q3_QUANT_Q4_K && a->qtype != Q3_QUANT_Q4_K_TILED)
+        return q3_fail(error, error_len,
+                       "fused q/k/v projection: weights must be Q4_K (GGUF or tiled order)");
+    if (a->hidden == 0 || a->hidden % Q3_QUANT_QK_K)
+        return q3_fail(error, error_len,
+                       "fused q/k/v projection: hidden size must be a multiple of 256");
+    if (((uintptr_t)a->wq | (uintptr_t)a->wk | (uintptr_t)a->wv | (uintptr_t)a->x_f16) & 15u)
+        return q3_fail(error, error_len,
+                       "fused q/k/v projection: pointers must be 16-byte aligned");
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g.device);
+    const uint32_t heads = a->n_q_heads + 2u * a->n_kv_heads;
+    LinearParams p = {};
+    p.out = nullptr;
+    p.M = a->tokens;
+    p.N = heads * 128u;
+    p.K = a->hidden;
+    p.NT = choose_token_tile(p.M, p.N, sms);
+    p.out_type = Q3_OUT_F16;
+    p.status = g.status_dev;
+    p.w_tiled = a->qtype == Q3_QUANT_Q4_K_TILED ? 1u : 0u;
+    p.f.seg_end[0] = a->n_q_heads;
+    p.f.seg_end[1] = a->n_q_heads + a->n_kv_heads;
+    p.f.seg_end[2] = heads;
+    p.f.n_q_heads = a->n_q_heads;
+    p.f.norm_w = a->norm_w;
+    p.f.eps = a->eps;
+    p.f.rope_table = (const float2 *)a->rope_table;
+    p.f.rope_pos = a->rope_pos;
+    p.f.dst_page = a->dst_page;
+    p.f.dst_slot = a->dst_slot;
+    p.f.q_out = (__half *)a->q_out;
+    p.f.k_pool = (__half *)a->k_pool;
+    p.f.v_pool = (__half *)a->v_pool;
+    p.f.num_pages = a->num_pages;
+    CUtensorMap x_map, w_map[3];
+    if (!q3_encode_tmap_2d(&x_map, a->x_f16, p.K, p.M, 64, p.NT, error, error_len)) return false;
+    const uint32_t slot = Smem<4>::kRowBytes;
+    const uint64_t row_bytes = (uint64_t)(p.K / Q3_QUANT_QK_K) * slot;
+    const void *w[3] = {a->wq, a->wk, a->wv};
+    const uint64_t n[3] = {a->n_q_heads * 128ull, a->n_kv_heads * 128ull, a->n_kv_heads * 128ull};
+    for (int i = 0; i < 3; i++) {
+        const bool ok = p.w_tiled
+                            ? q3_encode_tmap_bytes_2d(&w_map[i], w[i], 256, row_bytes * n[i] / 256,
+                                                      256, Smem<4>::kTiledRows, error, error_len)
+                            : q3_encode_tmap_bytes_2d(&w_map[i], w[i], row_bytes, n[i], slot, 128,
+                                                      error, error_len);
+        if (!ok) return false;
+    }
+    const uint32_t n_tiles = ((p.M + p.NT - 1) / p.NT) * heads;
+    const uint32_t grid = n_tiles < (uint32_t)sms ? n_tiles : (uint32_t)sms;
+    q4k_linear_tc_kernel<4, true><<<grid, kThreads, Smem<4, true>::kTotal, stream>>>(
+        x_map, w_map[0], w_map[1], w_map[2], p);
+    Q3_LAUNCH_CHECK("fused q/k/v projection launch failed");
+    return true;
+}
 
 extern "C" bool q3_q4_linear_bind_geometry(uint32_t qtype, uint32_t gguf_rows_dim0,
                                            uint32_t gguf_cols_dim1,
@@ -682,12 +909,16 @@ extern "C" bool q3_cuda_q4k_linear_init(int device, size_t max_tokens, int64_t m
         return q3_fail(error, error_len, "q3_q4_linear: no CUDA device");
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) return q3_fail_cuda(error, error_len, "q3_q4_linear: cudaSetDevice", e);
-    e = cudaFuncSetAttribute(q4k_linear_tc_kernel<4>,
+    e = cudaFuncSetAttribute(q4k_linear_tc_kernel<4, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<4>::kTotal);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(q4k_linear_tc_kernel<6>,
+        e = cudaFuncSetAttribute(q4k_linear_tc_kernel<6, false>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)Smem<6>::kTotal);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(q4k_linear_tc_kernel<4, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)Smem<4, true>::kTotal);
     if (e == cudaSuccess) e = cudaGetSymbolAddress((void **)&g.status_dev, q3_linear_status_word);
     if (e == cudaSuccess) e = cudaMemset(g.status_dev, 0, sizeof(uint32_t));
     if (e == cudaSuccess && !g.ev_begin) {

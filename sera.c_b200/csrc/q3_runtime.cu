@@ -660,25 +660,28 @@ extern "C" q3_prefix_kv *q3_prefix_create_with_pages(q3_attn_runtime *rt,
                       "q3_prefix_create_with_pages");
 }
 
-extern "C" bool q3_prefix_prefill_layer(q3_prefix_kv *prefix, uint32_t layer,
-                                        const void *q, const void *k,
-                                        const void *v, uint32_t tokens, void *out,
-                                        char *error, size_t error_len) {
-    q3_clear_error(error, error_len);
-    if (!prefix || !q || !k || !v || !out || tokens == 0)
-        return q3_fail(error, error_len, "q3_prefix_prefill_layer: invalid argument");
+/* Validation and the chunk's schedule, shared by the two prefill entries. */
+static q3_stage *prefill_prepare(q3_prefix_kv *prefix, uint32_t layer, uint32_t tokens,
+                                 char *error, size_t error_len) {
     q3_attn_runtime *rt = prefix->rt;
-    if (!q3_use_device(rt, error, error_len)) return false;
-    if (prefix->sealed)
-        return q3_fail(error, error_len, "q3_prefix_prefill_layer: prefix already sealed");
-    if (layer >= rt->cfg.num_layers)
-        return q3_fail(error, error_len, "q3_prefix_prefill_layer: layer out of range");
-    if ((uint64_t)prefix->token_count + tokens > prefix->capacity)
-        return q3_fail(error, error_len,
-                       "q3_prefix_prefill_layer: token_count exceeds capacity");
-    if (tokens > rt->cfg.max_tokens)
-        return q3_fail(error, error_len,
-                       "q3_prefix_prefill_layer: token_count exceeds runtime capacity");
+    if (!q3_use_device(rt, error, error_len)) return NULL;
+    if (prefix->sealed) {
+        q3_fail(error, error_len, "q3_prefix_prefill_layer: prefix already sealed");
+        return NULL;
+    }
+    if (layer >= rt->cfg.num_layers) {
+        q3_fail(error, error_len, "q3_prefix_prefill_layer: layer out of range");
+        return NULL;
+    }
+    if ((uint64_t)prefix->token_count + tokens > prefix->capacity) {
+        q3_fail(error, error_len, "q3_prefix_prefill_layer: token_count exceeds capacity");
+        return NULL;
+    }
+    if (tokens > rt->cfg.max_tokens) {
+        q3_fail(error, error_len,
+                "q3_prefix_prefill_layer: token_count exceeds runtime capacity");
+        return NULL;
+    }
     q3_stage *st = prefix->stage;
     const uint32_t base = prefix->token_count;
     /* The schedule depends only on (base, tokens): built for the first layer
@@ -696,16 +699,100 @@ extern "C" bool q3_prefix_prefill_layer(q3_prefix_kv *prefix, uint32_t layer,
                                pos.data(), prefix->pages, (uint32_t)prefix->pages.size(),
                                (uint32_t)rt->num_sms, rt->part_slots, false, error,
                                error_len))
-            return false;
-        if (!q3_stage_upload(st, s, pos, dpage, dslot, error, error_len)) return false;
+            return NULL;
+        if (!q3_stage_upload(st, s, pos, dpage, dslot, error, error_len)) return NULL;
         st->chunk_valid = true;
         st->chunk_base = base;
         st->chunk_tokens = tokens;
     }
+    return st;
+}
+
+extern "C" bool q3_prefix_prefill_layer(q3_prefix_kv *prefix, uint32_t layer,
+                                        const void *q, const void *k,
+                                        const void *v, uint32_t tokens, void *out,
+                                        char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!prefix || !q || !k || !v || !out || tokens == 0)
+        return q3_fail(error, error_len, "q3_prefix_prefill_layer: invalid argument");
+    q3_attn_runtime *rt = prefix->rt;
+    q3_stage *st = prefill_prepare(prefix, layer, tokens, error, error_len);
+    if (!st) return false;
     if (!q3_launch_kvwrite(rt, layer, q, k, v, tokens, st->rope_pos, st->dst_page,
                            st->dst_slot, rt->q2, error, error_len))
         return false;
     return q3_launch_attention(rt, layer, st, out, error, error_len);
+}
+
+/* The q/k/v projection of the layer with norm + RoPE + page write as its
+ * epilogue, then attention: two launches, and q, k, v never exist as tensors. */
+static bool projected_layer(q3_attn_runtime *rt, uint32_t layer, const q3_qkv_weights *w,
+                            const void *x_f16, uint32_t tokens, const q3_stage *st, void *out,
+                            char *error, size_t error_len) {
+    const q3_attn_config &c = rt->cfg;
+    if (w->qtype_q != w->qtype_k || w->qtype_q != w->qtype_v)
+        return q3_fail(error, error_len,
+                       "fused q/k/v projection: the three weights must have one quantisation "
+                       "type and layout (project them one by one otherwise)");
+    const size_t layer_off = (size_t)layer * c.n_kv_heads * c.num_pages * Q3_PAGE * Q3_D;
+    q3_qkv_fused_args a;
+    a.wq = w->wq;
+    a.wk = w->wk;
+    a.wv = w->wv;
+    a.qtype = w->qtype_q;
+    a.hidden = w->hidden;
+    a.n_q_heads = c.n_heads;
+    a.n_kv_heads = c.n_kv_heads;
+    a.x_f16 = x_f16;
+    a.tokens = tokens;
+    a.norm_w = rt->qk_norm_w + (size_t)layer * 2 * Q3_D;
+    a.eps = c.rms_eps;
+    a.rope_table = rt->rope_table;
+    a.rope_pos = st->rope_pos;
+    a.dst_page = st->dst_page;
+    a.dst_slot = st->dst_slot;
+    a.q_out = rt->q2;
+    a.k_pool = rt->k_pool + layer_off;
+    a.v_pool = rt->v_pool + layer_off;
+    a.num_pages = c.num_pages;
+    q3_phase_begin(rt, Q3_PHASE_KVWRITE);
+    const bool ok = q3_launch_qkv_fused(&a, rt->stream, error, error_len);
+    q3_phase_end(rt);
+    if (!ok) return false;
+    rt->n_launch++;
+    return q3_launch_attention(rt, layer, st, out, error, error_len);
+}
+
+extern "C" bool q3_prefix_prefill_layer_projected(q3_prefix_kv *prefix, uint32_t layer,
+                                                  const q3_qkv_weights *weights,
+                                                  const void *x_f16, uint32_t tokens,
+                                                  void *out, char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!prefix || !weights || !weights->wq || !weights->wk || !weights->wv || !x_f16 ||
+        !out || tokens == 0)
+        return q3_fail(error, error_len,
+                       "q3_prefix_prefill_layer_projected: invalid argument");
+    q3_stage *st = prefill_prepare(prefix, layer, tokens, error, error_len);
+    if (!st) return false;
+    return projected_layer(prefix->rt, layer, weights, x_f16, tokens, st, out, error,
+                           error_len);
+}
+
+extern "C" bool q3_suffix_attention_layer_projected(q3_pack_plan *plan, uint32_t layer,
+                                                    const q3_qkv_weights *weights,
+                                                    const void *x_f16, void *out,
+                                                    char *error, size_t error_len) {
+    q3_clear_error(error, error_len);
+    if (!plan || !weights || !weights->wq || !weights->wk || !weights->wv || !x_f16 || !out)
+        return q3_fail(error, error_len,
+                       "q3_suffix_attention_layer_projected: invalid argument");
+    q3_attn_runtime *rt = plan->prefix->rt;
+    if (!q3_use_device(rt, error, error_len)) return false;
+    if (layer >= rt->cfg.num_layers)
+        return q3_fail(error, error_len,
+                       "q3_suffix_attention_layer_projected: layer out of range");
+    return projected_layer(rt, layer, weights, x_f16, plan->tokens, plan->stage, out, error,
+                           error_len);
 }
 
 extern "C" bool q3_prefix_advance(q3_prefix_kv *prefix, uint32_t tokens,
