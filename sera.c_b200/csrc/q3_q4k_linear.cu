@@ -28,6 +28,10 @@
  * Operand rounding: scale = f16(d*sc), offset = f16(dmin*m), element =
  * f16(fma(q, scale, -offset)); activations are f16; accumulation is fp32.
  *
+ * A second instantiation serves the q/k/v projection of a layer (three weights,
+ * a feature tile = one head): its drain normalises and rotates the heads and
+ * writes f16 queries and K/V pages instead of an output tensor (FusedEpilogue).
+ *
  * Every wait is bounded: on expiry the CTA raises its abort flag, all roles
  * drain, the status word gets bit 0 and tensor memory is released.
  */

@@ -54,6 +54,23 @@ def test_case_fp32_output(pkg, name):
     assert np.array_equal(_candidate_argmax(got, case), _candidate_argmax(ref, case))
 
 
+@pytest.mark.parametrize("name", _cases.GOLDEN_CASES + ["long_prefix"])
+def test_case_with_pages_in_allocation_order(pkg, name):
+    """Pages as the pool hands them out (ascending): key tiles whose eight pages
+    follow one another are fetched as one copy per half, through the second
+    tensor map of the pool - the path the other tests (permuted pages) do not
+    take."""
+    case = (harness.rounded_case(_cases.Case("long_prefix", 1500, [40, 3, 33, 17], n_heads=16,
+                                             n_kv_heads=2, seed=21, unit_norm_weights=False))
+            if name == "long_prefix" else harness.rounded_case(_cases.make_case(name)))
+    ref = oracle.run_case(case)["out"]
+    got = harness.run_case_native(pkg, case, out_fp32=True, permute_pages=False)
+    assert np.abs(got - ref).max() <= ATOL
+    chunked = harness.run_case_native(pkg, case, out_fp32=True, permute_pages=False,
+                                      prefill_chunks=[case.P - case.P // 3, case.P // 3])
+    assert np.abs(chunked - ref).max() <= ATOL
+
+
 @pytest.mark.parametrize("name", _cases.GOLDEN_CASES)
 def test_case_bf16_output(pkg, name):
     case = harness.rounded_case(_cases.make_case(name))

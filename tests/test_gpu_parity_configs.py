@@ -33,7 +33,10 @@ def pkg():
     return entry.load_package()
 
 
-def test_stack_layer_p32768_b128x16_sampled_rows(pkg):
+@pytest.mark.parametrize("page_order", ["permuted", "consecutive"])
+def test_stack_layer_p32768_b128x16_sampled_rows(pkg, page_order):
+    """`consecutive`: the pool's own allocation order, where the kernel fetches the
+    eight pages of a key tile as one copy per half; `permuted`: one copy per page."""
     P, B, n, H, Hkv, D = 32768, 128, 16, 64, 8, 128
     S = B * n
     g = torch.Generator().manual_seed(0)
@@ -46,9 +49,10 @@ def test_stack_layer_p32768_b128x16_sampled_rows(pkg):
     num_pages = n_pp + B + 8
     rt = pkg.Runtime(num_layers=1, n_heads=H, n_kv_heads=Hkv, max_positions=P + 64,
                      max_tokens=S, num_pages=num_pages, out_fp32=True)
-    perm = np.random.default_rng(1).permutation(num_pages).astype(np.uint32)
+    perm = (np.random.default_rng(1).permutation(num_pages) if page_order == "permuted"
+            else np.arange(num_pages)).astype(np.uint32)
     rt.alloc_pages(num_pages)
-    rt.free_pages(perm[n_pp:])
+    rt.free_pages(perm[n_pp:][::-1].copy())
     prefix = pkg.Prefix(rt, P, pages=perm[:n_pp])
     pk, pv = rt.pool()
     idx = torch.from_numpy(perm[:n_pp].astype(np.int64)).cuda()
