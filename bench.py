@@ -192,23 +192,26 @@ def run_ours(args):
     stream = rt.torch_stream()
 
     fused = world > 1 and args.gather == "copy"
-    pg = sharding.PeerGather(TOKENS, hq, D, torch.bfloat16, device) if fused else None
+    GD = max(2, args.gather_depth)
+    pg = (sharding.PeerGather(TOKENS, hq, D, torch.bfloat16, device, depth=GD)
+          if fused else None)
 
     def step_device():
         if fused:
             # each layer writes this rank's slot of its gathered buffer; copy
             # engines push the slot to the other ranks on a side stream and
-            # publish flags; buffer b is reused by layer l+2 only after every
-            # rank's layer-l rows have arrived here (device-side flag wait, no
-            # collective). Sequence numbers are step-relative; the device-side
-            # counter advanced at the end makes every step (or graph replay)
-            # publish fresh ones
+            # publish flags; a buffer is reused GD layers later, only after every
+            # rank's rows of the layer it held have arrived here (device-side
+            # flag wait, no collective): with GD buffers a rank may run GD - 1
+            # layers ahead of the slowest one. Sequence numbers are
+            # step-relative; the device-side counter advanced at the end makes
+            # every step (or graph replay) publish fresh ones
             for l in range(L):
-                if l >= 2:
-                    rt.wait_gathered(pg.peers(l), l - 1)
+                if l >= GD:
+                    rt.wait_gathered(pg.peers(l), l - GD + 1)
                 plan.attention_layer_gathered(l, dq_[l], dk_[l], dv_[l], pg.peers(l), l + 1)
-            rt.wait_gathered(pg.peers(L - 2), L - 1)
-            rt.wait_gathered(pg.peers(L - 1), L)
+            for l in range(max(0, L - GD), L):
+                rt.wait_gathered(pg.peers(l), l + 1)
             rt.gather_advance(L)
             return
         works = [None, None]
@@ -228,12 +231,12 @@ def run_ours(args):
             # the whole step as a host caller sees it: host buffers in, the
             # exchange between the ranks, this rank's rows back to the host
             for l in range(L):
-                if l >= 2:
-                    rt.wait_gathered(pg.peers(l), l - 1)
+                if l >= GD:
+                    rt.wait_gathered(pg.peers(l), l - GD + 1)
                 plan.attention_layer_gathered_host(l, hq_[l], hk_[l], hv_[l], pg.peers(l),
                                                    l + 1, out_host)
-            rt.wait_gathered(pg.peers(L - 2), L - 1)
-            rt.wait_gathered(pg.peers(L - 1), L)
+            for l in range(max(0, L - GD), L):
+                rt.wait_gathered(pg.peers(l), l + 1)
             rt.gather_advance(L)
             return
         for l in range(L):
@@ -484,8 +487,10 @@ def case_prefill(pkg, torch, device, T=4096, reps=20):
     return res
 
 
-def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20, n_kv_heads=HKV):
-    """Shared-prefix + packed-suffix attention, one layer, prefix resident."""
+def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20, n_kv_heads=HKV,
+                 permute=False):
+    """Shared-prefix + packed-suffix attention, one layer, prefix resident; pages
+    in the pool's allocation order, or (`permute`) in a random order."""
     peaks = measured_peaks()
     g = torch.Generator(device=device).manual_seed(0)
     rnd = lambda *shape: torch.randn(*shape, generator=g, device=device).to(torch.bfloat16)
@@ -494,7 +499,14 @@ def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20, n_kv_heads=HKV
     rt = pkg.Runtime(num_layers=1, n_heads=8 * n_kv_heads, n_kv_heads=n_kv_heads, max_positions=P + n + 8,
                      max_tokens=S, num_pages=P // 16 + ppb * B + 4, device=device.index)
     rt.enable_timing(16 * reps + 64)
-    prefix = pkg.Prefix(rt, P)
+    if permute:
+        num_pages = P // 16 + ppb * B + 4
+        perm = np.random.default_rng(1).permutation(num_pages).astype(np.uint32)
+        rt.alloc_pages(num_pages)
+        rt.free_pages(perm[P // 16:])
+        prefix = pkg.Prefix(rt, P, pages=perm[:P // 16])
+    else:
+        prefix = pkg.Prefix(rt, P)
     kp, vp = rt.pool()
     kp.normal_(generator=g)
     vp.normal_(generator=g)
@@ -507,7 +519,8 @@ def case_cascade(pkg, torch, device, P=8192, B=64, n=24, reps=20, n_kv_heads=HKV
     ms, ph = _time_calls(torch, rt, lambda: plan.attention_layer(0, q, k, v, out), reps)
     flops = 4 * D * 8 * n_kv_heads * (S * P + B * n * (n + 1) // 2)
     k_ms = ph["attention"][0] / max(ph["attention"][1], 1)
-    res = {"prefix": P, "branches": B, "suffix": n, "kv_heads": n_kv_heads, "ms": ms,
+    res = {"prefix": P, "branches": B, "suffix": n, "kv_heads": n_kv_heads,
+           "pages": "random order" if permute else "allocation order", "ms": ms,
            "suffix_tokens_per_s": S / ms * 1e3, "tflops": flops / ms / 1e9,
            "attention_kernel_ms": k_ms, "attention_kernel_tflops": flops / k_ms / 1e9,
            "frac_of_bf16_burst_peak": flops / k_ms / 1e9 / peaks["tflops_burst"],
@@ -555,6 +568,7 @@ CASES = {
     "cascade_p8192_b64x24": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, 8192, 64, 24, reps),
     "stack_layer_p32768_b128x16": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, PREFIX, BRANCHES, SUFFIX, reps),
     "stack_layer_1kvhead": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, PREFIX, BRANCHES, SUFFIX, reps, 1),
+    "stack_layer_permuted_pages": lambda pkg, torch, dev, reps: case_cascade(pkg, torch, dev, PREFIX, BRANCHES, SUFFIX, reps, permute=True),
     "decode_256seq": lambda pkg, torch, dev, reps: case_decode(pkg, torch, dev, 256, reps),
     "decode_64seq": lambda pkg, torch, dev, reps: case_decode(pkg, torch, dev, 64, reps),
 }
@@ -1179,6 +1193,9 @@ def main():
                          "of this rank's rows into the other ranks' buffers plus flags, on a "
                          "side stream (default), 'nccl' = all_gather_into_tensor overlapped on "
                          "a side stream, 'none' = skipped (diagnostic)")
+    ap.add_argument("--gather-depth", type=int, default=3,
+                    help="gathered buffers per rank at N > 1 (a rank may run depth - 1 layers "
+                         "ahead of the slowest)")
     ap.add_argument("--case", choices=sorted(CASES), default=None,
                     help="run only this single-layer case (for profiler captures)")
     ap.add_argument("--reps", type=int, default=5)

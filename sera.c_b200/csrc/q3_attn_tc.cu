@@ -29,11 +29,12 @@
  *   O += P V    tcgen05.mma, A = P from tensor memory, B = V pages (smem,
  *               MN-major), D = O in tensor memory (fp32).
  *   TMEM        S [0,128), P0 [128,192), P1 [192,256), O0 [256,384), O1 [384,512).
- *   K/V pages   4 KiB per page per head, fetched by TMA (two 64-column boxes,
- *               128-byte swizzle) straight into the UMMA operand layout; the
- *               eight pages of a key tile as two 128-row boxes when they follow
- *               one another in the pool. Every CTA issues its own loads, from
- *               this GPU's memory only.
+ *   K/V pages   4 KiB per page per head, fetched by TMA (128-byte swizzle)
+ *               straight into the UMMA operand layouts: a K page as two
+ *               64-column boxes - the eight pages of a key tile as two 128-row
+ *               boxes when they follow one another in the pool -, a V page as
+ *               one 3-D box holding both column halves. Every CTA issues its
+ *               own loads, from this GPU's memory only.
  * Warp roles: 0 = TMA producer, 1 = issuer of the S MMAs (owns the TMEM
  * allocation), 2 / 3 = issuers of the PV MMAs of M tile 0 / 1 (three threads
  * issue, each waiting on its own events in order, so that no event waits
@@ -262,9 +263,8 @@ __device__ __forceinline__ void store_row_chunk(const AttnParams &p, size_t off,
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map,
-                    const __grid_constant__ CUtensorMap k_map_tile,
-                    const __grid_constant__ CUtensorMap v_map_tile, const AttnParams p) {
+                    const __grid_constant__ CUtensorMap v_map_page,
+                    const __grid_constant__ CUtensorMap k_map_tile, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Misc *misc = reinterpret_cast<Misc *>(smem + kSmemMisc);
@@ -310,9 +310,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         if (lane == 0) {
             prefetch_tmap(&q_map);
             prefetch_tmap(&k_map);
-            prefetch_tmap(&v_map);
+            prefetch_tmap(&v_map_page);
             prefetch_tmap(&k_map_tile);
-            prefetch_tmap(&v_map_tile);
         }
         uint32_t it = 0;          /* K tiles armed so far */
         uint32_t v_armed = 0;     /* V tiles armed so far */
@@ -347,12 +346,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             }
             q_armed++;
             /* Arm the K and V loads of one key tile: lanes 0..7 fetch one page
-             * each (two 64-column boxes) from pool row `row`; when the eight
-             * pages follow one another in the pool (`run`), lane 0 fetches
-             * them as two boxes of 128 rows. A copy costs the issuing warp
-             * about 60 clocks whatever its size, one lane after the other:
-             * 32 page copies per key tile are 2 k clocks of this warp, more
-             * than the tensor work of the tile. */
+             * each from pool row `row` (K: two 64-column boxes; V: one box with
+             * both halves); when the eight pages follow one another in the pool
+             * (`run`), lane 0 fetches K as two boxes of 128 rows. A copy costs
+             * the issuing warp about 60 clocks whatever its size, one lane after
+             * the other: 32 page copies per key tile were 2 k clocks of this
+             * warp, more than the tensor work of the tile; now 24, or 10 in a run. */
             auto arm_tile = [&](int32_t row, bool run) {
                 const uint32_t stage = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
@@ -375,17 +374,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 if (!alive) return;
                 if (lane == 0) mbar_arrive_expect_tx(&bar.v_full[stage], kTileBytes);
                 __syncwarp();
-                if (run) {
-                    if (lane == 0) {
-                        uint8_t *dst = smem + kSmemV + stage * kTileBytes;
-                        tma_load_2d(dst, &v_map_tile, 0, row, &bar.v_full[stage]);
-                        tma_load_2d(dst + kHalfBytes, &v_map_tile, 64, row, &bar.v_full[stage]);
-                    }
-                } else if (lane < 8) {
-                    uint8_t *dst = smem + kSmemV + stage * kTileBytes + lane * kPageHalfBytes;
-                    tma_load_2d(dst, &v_map, 0, row, &bar.v_full[stage]);
-                    tma_load_2d(dst + kHalfBytes, &v_map, 64, row, &bar.v_full[stage]);
-                }
+                /* V: one copy per page, both column halves ([half][16 keys][128 B],
+                 * 4 KiB per page). A PV MMA step consumes one page, so its operand
+                 * descriptor can point at any page; K, whose MMA walks all 128
+                 * keys of a column half at one stride, cannot be laid out so. */
+                if (lane < 8)
+                    tma_load_3d(smem + kSmemV + stage * kTileBytes + lane * 2u * kPageHalfBytes,
+                                &v_map_page, 0, row, 0, &bar.v_full[stage]);
                 v_armed++;
             };
             const uint32_t row_base = p.pool_row_base + seg.kv_head * p.num_pages * Q3_PAGE;
@@ -558,14 +553,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                             alive = wait_or_abort(&bar.v_full[stage], (it / kStages) & 1u, misc);
                         if (!alive) break;
                         tc_fence_after();
-                        /* keys [64*half, 64*half+64): 4 steps of K = 16 keys; V is
-                         * MN-major (64-column blocks 16 KiB apart, 16-key groups
-                         * 2 KiB apart) */
+                        /* keys [64*half, 64*half+64): 4 steps of K = 16 keys = one
+                         * page each; V is MN-major (a page is 4 KiB: its two
+                         * 64-column blocks 2 KiB apart, 8-key groups 1 KiB apart) */
 #pragma unroll
                         for (uint32_t ks = half * 4; ks < half * 4 + 4; ks++)
                             umma_ts(tmem + kColO + q * 128u, tmem + kColP + q * 64u + ks * 8u,
-                                    umma_desc(v_addr + stage * kTileBytes + ks * 2048u,
-                                              kHalfBytes, 1024),
+                                    umma_desc(v_addr + stage * kTileBytes + ks * 4096u,
+                                              2u * 1024u, 1024),
                                     idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                         umma_commit(&bar.pv_done[q][half]);
                     }
@@ -965,7 +960,7 @@ bool q3_launch_attention(q3_attn_runtime *rt, uint32_t layer, const q3_stage *st
     p.status = rt->status_dev;
     q3_phase_begin(rt, Q3_PHASE_ATTENTION);
     attention_tc_kernel<<<st->grid, kThreads, kSmemTotal, rt->stream>>>(
-        q_map, rt->k_map, rt->v_map, rt->k_map_tile, rt->v_map_tile, p);
+        q_map, rt->k_map, rt->v_map_page, rt->k_map_tile, p);
     q3_phase_end(rt);
     Q3_LAUNCH_CHECK("attention_tc launch failed");
     rt->n_launch++;

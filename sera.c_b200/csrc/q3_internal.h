@@ -64,8 +64,8 @@ struct q3_attn_runtime {
     __half *v_pool;
     CUtensorMap k_map; /* 2-D {128, L*Hkv*num_pages*16}, box {64,16}, SW128 */
     CUtensorMap v_map;
-    CUtensorMap k_map_tile; /* same tensors, box {64,128}: eight consecutive pages in one copy */
-    CUtensorMap v_map_tile;
+    CUtensorMap k_map_tile; /* same tensor, box {64,128}: eight consecutive pages in one copy */
+    CUtensorMap v_map_page; /* 3-D {64, rows, 2 halves}, box {64,16,2}: a page's two halves in one copy */
     std::vector<uint32_t> free_pages;
 
     float *qk_norm_w;  /* device [L][2][128] */
@@ -295,6 +295,8 @@ bool q3_encode_tmap_2d(CUtensorMap *map, const void *base, uint64_t inner,
 bool q3_encode_tmap_bytes_2d(CUtensorMap *map, const void *base, uint64_t row_bytes,
                              uint64_t rows, uint32_t box_bytes, uint32_t box_rows,
                              char *error, size_t error_len);
+bool q3_encode_tmap_page(CUtensorMap *map, const void *base, uint64_t rows, char *error,
+                         size_t error_len);
 bool q3_encode_tmap_q(CUtensorMap *map, const void *base, uint32_t n_heads,
                       uint32_t tokens, char *error, size_t error_len);
 

@@ -102,6 +102,30 @@ bool q3_encode_tmap_bytes_2d(CUtensorMap *map, const void *base, uint64_t row_by
 
 /* Query workspace [tokens][n_heads][128] f16 viewed as {128, n_heads, tokens};
  * box {64, 8, 16}: 16 tokens x 8 heads of one KV group, half a head row. */
+/* A page pool [rows][128] f16 seen as {64 columns, rows, 2 column halves}: the
+ * stride of the third dimension (128 B) is smaller than that of the second
+ * (256 B), which the encoder accepts. One box {64, 16, 2} is a whole page,
+ * written as [half][16 rows][128 B] - byte for byte what the two 64-column
+ * boxes of the 2-D map write into two consecutive 2 KiB blocks. */
+bool q3_encode_tmap_page(CUtensorMap *map, const void *base, uint64_t rows, char *error,
+                         size_t error_len) {
+    encode_tiled_fn fn = get_encode_fn();
+    if (!fn) return q3_fail(error, error_len, "cuTensorMapEncodeTiled unavailable");
+    cuuint64_t dims[3] = {64, rows, 2};
+    cuuint64_t strides[2] = {Q3_D * 2, 128};
+    cuuint32_t box[3] = {64, Q3_PAGE, 2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, (void *)base, dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        if (error && error_len)
+            snprintf(error, error_len, "cuTensorMapEncodeTiled(page) failed (%d)", (int)r);
+        return false;
+    }
+    return true;
+}
+
 bool q3_encode_tmap_q(CUtensorMap *map, const void *base, uint32_t n_heads,
                       uint32_t tokens, char *error, size_t error_len) {
     encode_tiled_fn fn = get_encode_fn();
@@ -275,8 +299,7 @@ extern "C" q3_attn_runtime *q3_attn_create(const q3_attn_config *config,
                            error_len) ||
         !q3_encode_tmap_2d(&rt->k_map_tile, rt->k_pool, Q3_D, pool_rows, 64, 8 * Q3_PAGE, error,
                            error_len) ||
-        !q3_encode_tmap_2d(&rt->v_map_tile, rt->v_pool, Q3_D, pool_rows, 64, 8 * Q3_PAGE, error,
-                           error_len)) {
+        !q3_encode_tmap_page(&rt->v_map_page, rt->v_pool, pool_rows, error, error_len)) {
         q3_attn_destroy(rt);
         return NULL;
     }
