@@ -134,6 +134,28 @@ def shard_inputs(torch, layer, rank, n_gpus, device):
     return sharding.slice_heads(q, k, v, rank, n_gpus)
 
 
+def bind_to_gpu_cpus(torch, device):
+    """Multi-rank runs: keep this process (and so its pinned host buffers, by
+    first touch) on the CPUs NVML lists as local to its GPU. Eight ranks that
+    copy from host memory of the wrong socket share one inter-socket link.
+    Returns the number of CPUs kept, or None when NVML gives no answer."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        pr = torch.cuda.get_device_properties(device)
+        bus = "%08X:%02X:%02X.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, m in enumerate(words) for b in range(64) if (m >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -150,6 +172,7 @@ def run_ours(args):
         raise SystemExit("KV-head sharding needs --gpus in {1,2,4,8}")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    numa = bind_to_gpu_cpus(torch, device) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     entry.build()
@@ -337,7 +360,8 @@ def run_ours(args):
                        "heads": "%d/%d x %d" % (H, HKV, D), "kv": "paged f16, page 16, permuted table",
                        "sharding": "kv_heads/%d + all-gather per layer (%s)" % (
                            n_gpus, args.gather if n_gpus > 1 else "single GPU"),
-                       "l2": "inputs larger than L2 (8.6 GB of KV per step)"},
+                       "l2": "inputs larger than L2 (8.6 GB of KV per step)",
+                       "host_cpus_bound_to_gpu": numa},
             "tflops": FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12,
             "e2e": {"value": TOKENS / (e2e_ms_per_step * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": qkv_bytes, "d2h_bytes_per_step": out_bytes,
