@@ -7,7 +7,7 @@
 
 /* start-up cost of a segment, in quarter key tiles */
 #ifndef Q3_SCHED_SEGMENT_COST
-#define Q3_SCHED_SEGMENT_COST 8
+#define Q3_SCHED_SEGMENT_COST 10
 #endif
 
 static bool sched_fail(char *error, size_t error_len, const char *msg) {
