@@ -103,8 +103,8 @@ def _check_schedule(pkg, row_tag, row_lp, n_kv, shared_len, ppb, nb, ctas, locks
         assert s.shared_tiles == shared_tiles
         key = (s.kv_head, s.tok0)
         cover.setdefault(key, []).append((s.tile_begin, s.tile_end, s.partial_slot))
-        # cost of a segment: its key tiles + a fixed start-up of 1.5 tiles
-        per_cta[s.cta] = per_cta.get(s.cta, 0) + s.tile_end - s.tile_begin + 1.5
+        # cost of a segment as the scheduler charges it: its key tiles + a fixed start-up of 2.5 tiles
+        per_cta[s.cta] = per_cta.get(s.cta, 0) + s.tile_end - s.tile_begin + 2.5
     assert len(cover) == n_kv * n_tt
     slots = set()
     n_cut = 0
